@@ -64,12 +64,21 @@ class LayerCall:
 
     `layer` is an index into the model's layers (a layer may be named twice);
     `cache` is the index of the cache slot its mixer reads (another layer's slot lets it
-    read that layer's keys and values); `append` says whether this call writes the
-    step's new entries into that slot.
+    read that layer's keys and values; a layer that runs several times with a cache of its
+    own each time names a different slot per call - slots need not be layer numbers);
+    `append` says whether this call writes the step's new entries into that slot;
+    `state` is the index of the fixed-size state the call carries (-1: the layer's number);
+    `add_vector`, if given, is (tensor name, row): that row of one of the plan's
+    `stream_vectors` is added to the residual stream right before the call.
     """
     layer: int
     cache: int
     append: bool = True
+    state: int = -1
+    add_vector: Optional[Tuple[str, int]] = None
+
+    def state_slot(self) -> int:
+        return self.layer if self.state < 0 else self.state
 
 
 @dataclass(frozen=True)
@@ -84,6 +93,9 @@ class ModelPlan:
     embedding_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm."
     head_name: str = "lm_head.weight"
+    logit_scale: float = 1.0                                    # logits = head x * logit_scale
+    # float32 tables [rows, hidden] whose rows the order may add to the stream: (name, rows)
+    stream_vectors: Tuple[Tuple[str, int], ...] = ()
 
 
 # --------------------------------------------------------------------------------------

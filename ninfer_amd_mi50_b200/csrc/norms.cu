@@ -1,0 +1,216 @@
+// Row-wise kernels beside those of elementwise.cu: a layer norm (mean taken off, weight, no
+// bias) fused with the residual sum; an RMS norm of a column slice; the gated RMS norm in
+// equal parts that follows a state-space mixer; a vector added to every row of the stream; a
+// sigmoid gate; rows gathered in the experts' order and scaled by their routing weight.
+//
+// All statistics are float32 whatever the activations' type.  The layer norm's variance is the
+// mean of the squared deviations from the mean (two passes over a row kept in shared memory),
+// not E[x^2] - mean^2.
+#define NF_CHAIN_CLASS 2
+#include "common.cuh"
+
+namespace nf {
+
+// h[t] += delta[t] (if delta); out[t] = (h[t] - mean) * rsqrt(var + eps) * w.
+// With `rows`, row r reads h[rows[r]] / delta[rows[r]], writes out[r] and leaves h alone.
+template <typename T, bool GATHER>
+__global__ void add_layernorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                     const int* __restrict__ rows, const float* __restrict__ w,
+                                     float eps, T* __restrict__ out, int hidden) {
+  extern __shared__ float row[];      // [hidden]
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  chain_release_if_small();
+  chain_wait(h, delta, rows);
+  const int src = GATHER ? rows[r] : r;
+  float* hr = h + (size_t)src * hidden;
+  const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  T* o = out + (size_t)r * hidden;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = hr[i];
+    if (dr) {
+      v += to_float(dr[i]);
+      if (!GATHER) hr[i] = v;
+    }
+    row[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, red) / (float)hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float d = row[i] - mean;
+    ss += d * d;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_float<T>((row[i] - mean) * inv * w[i]);
+}
+
+// out[t, 0:n] = x[t, col0:col0+n] * rsqrt(mean(x^2) + eps) * w   (w may be null: weight 1)
+template <typename T>
+__global__ void rms_norm_slice_kernel(const T* __restrict__ x, int ldx, int col0, int n,
+                                      const float* __restrict__ w, float eps, T* __restrict__ out, int ldo) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  chain_release_if_small();
+  chain_wait(x);
+  const T* xr = x + (size_t)t * ldx + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = to_float(xr[i]);
+    ss += v * v;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  T* o = out + (size_t)t * ldo;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    o[i] = from_float<T>(to_float(xr[i]) * inv * (w ? w[i] : 1.f));
+}
+
+// g = y * silu(z); each of `parts` equal parts of a row over its own root mean square; times w.
+// y float32 [T, inner]; z = zsrc[t, zcol0 + i]; out [T, inner].
+template <typename T>
+__global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ zsrc, int ldz,
+                                           int zcol0, const float* __restrict__ w, float eps,
+                                           T* __restrict__ out, int inner, int parts) {
+  extern __shared__ float row[];      // [inner / parts]
+  __shared__ float red[33];
+  const int t = blockIdx.x, part = blockIdx.y;
+  const int n = inner / parts, c0 = part * n;
+  chain_release_if_small();
+  chain_wait(y, zsrc);
+  const float* yr = y + (size_t)t * inner + c0;
+  const T* zr = zsrc + (size_t)t * ldz + zcol0 + c0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float z = to_float(zr[i]);
+    const float g = yr[i] * (z / (1.f + expf(-z)));
+    row[i] = g;
+    ss += g * g;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  T* o = out + (size_t)t * inner + c0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_float<T>(row[i] * inv * w[c0 + i]);
+}
+
+__global__ void add_row_vector_kernel(float* __restrict__ h, const float* __restrict__ vec, int hidden) {
+  chain_wait(h);
+  float* hr = h + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) hr[i] += vec[i];
+}
+
+// out[t, hd * n + i] = v[hd, t, i] * sigmoid(g[t, gcol0 + hd * n + i]):  v is laid out head by head
+// ([heads, T, n], what a batched product over heads leaves), out token by token.
+template <typename T>
+__global__ void heads_sigmoid_gate_kernel(const T* __restrict__ v, const T* __restrict__ g, int ldg, int gcol0,
+                                          T* __restrict__ out, int rows, int heads, int n) {
+  const int t = blockIdx.x;
+  chain_wait(v, g);
+  const int width = heads * n;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const int hd = c / n, i = c - hd * n;
+    const float gv = to_float(g[(size_t)t * ldg + gcol0 + c]);
+    const float vv = to_float(v[((size_t)hd * rows + t) * n + i]);
+    out[(size_t)t * width + c] = from_float<T>(vv * (1.f / (1.f + expf(-gv))));
+  }
+}
+
+// out[p] = scale[order[p]] * x[order[p] / div]: the tokens in the experts' order, each times the
+// weight of its (token, choice) pair.
+template <typename T>
+__global__ void scale_gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ order, int div,
+                                         const float* __restrict__ scale, T* __restrict__ out, int hidden,
+                                         int n_pairs) {
+  const int p = blockIdx.x;
+  chain_wait(x, order, scale);
+  const int pair = order[p];
+  T* o = out + (size_t)p * hidden;
+  if (pair < 0 || pair >= n_pairs) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(0.f);
+    return;
+  }
+  const float s = scale[pair];
+  const T* xr = x + (size_t)(pair / div) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(s * to_float(xr[i]));
+}
+
+}  // namespace nf
+
+using namespace nf;
+
+extern "C" int nf_add_layernorm(float* h, const void* delta, const int* rows, const float* w, float eps, void* out,
+                                int R, int hidden, int dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && hidden > 0, "add_layernorm: bad sizes R=%d hidden=%d", R, hidden);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  NF_REQUIRE(smem <= 160 * 1024, "add_layernorm: a row of %d does not fit shared memory", hidden);
+  const int threads = hidden >= 2048 ? 512 : 256;
+#define NF_LN(T, G)                                                                                         \
+  do {                                                                                                      \
+    if (smem > 48 * 1024)                                                                                   \
+      cudaFuncSetAttribute(add_layernorm_kernel<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_chained(add_layernorm_kernel<T, G>, dim3(R), dim3(threads), smem, stream, h, (const T*)delta, rows, w, \
+                   eps, (T*)out, hidden);                                                                   \
+  } while (0)
+  if (dtype == kF32) { if (rows) NF_LN(float, true); else NF_LN(float, false); }
+  else { if (rows) NF_LN(__nv_bfloat16, true); else NF_LN(__nv_bfloat16, false); }
+#undef NF_LN
+  return check_launch("add_layernorm");
+}
+
+extern "C" int nf_rms_norm_slice(const void* x, int ldx, int col0, int n, const float* w, float eps, void* out,
+                                 int ldo, int R, int dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && n > 0 && col0 >= 0 && col0 + n <= ldx && ldo >= n, "rms_norm_slice: bad sizes");
+  if (dtype == kF32)
+    launch_chained(rms_norm_slice_kernel<float>, dim3(R), dim3(128), 0, stream, (const float*)x, ldx, col0, n, w, eps, (float*)out, ldo);
+  else
+    launch_chained(rms_norm_slice_kernel<__nv_bfloat16>, dim3(R), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, col0, n, w, eps, (__nv_bfloat16*)out, ldo);
+  return check_launch("rms_norm_slice");
+}
+
+extern "C" int nf_gated_group_rmsnorm(const float* y, const void* z, int ldz, int zcol0, const float* w, float eps,
+                                      void* out, int R, int inner, int parts, int dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && inner > 0 && parts > 0 && inner % parts == 0, "gated_group_rmsnorm: %d does not split into %d parts", inner, parts);
+  const size_t smem = (size_t)(inner / parts) * sizeof(float);
+  NF_REQUIRE(smem <= 160 * 1024, "gated_group_rmsnorm: a part of %d does not fit shared memory", inner / parts);
+#define NF_GN(T)                                                                                               \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(gated_group_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_chained(gated_group_rmsnorm_kernel<T>, dim3(R, parts), dim3(256), smem, stream, y, (const T*)z, ldz, zcol0, \
+                   w, eps, (T*)out, inner, parts);                                                             \
+  } while (0)
+  if (dtype == kF32) NF_GN(float); else NF_GN(__nv_bfloat16);
+#undef NF_GN
+  return check_launch("gated_group_rmsnorm");
+}
+
+extern "C" int nf_add_row_vector(float* h, const float* vec, int R, int hidden, cudaStream_t stream) {
+  if (R == 0) return 0;
+  launch_chained(add_row_vector_kernel, dim3(R), dim3(256), 0, stream, h, vec, hidden);
+  return check_launch("add_row_vector");
+}
+
+extern "C" int nf_heads_sigmoid_gate(const void* v, const void* g, int ldg, int gcol0, void* out, int R, int heads,
+                                     int n, int dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(heads > 0 && n > 0 && gcol0 >= 0 && gcol0 + heads * n <= ldg, "heads_sigmoid_gate: bad sizes");
+  if (dtype == kF32)
+    launch_chained(heads_sigmoid_gate_kernel<float>, dim3(R), dim3(256), 0, stream, (const float*)v, (const float*)g, ldg, gcol0, (float*)out, R, heads, n);
+  else
+    launch_chained(heads_sigmoid_gate_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, stream, (const __nv_bfloat16*)v, (const __nv_bfloat16*)g, ldg, gcol0, (__nv_bfloat16*)out, R, heads, n);
+  return check_launch("heads_sigmoid_gate");
+}
+
+extern "C" int nf_scale_gather_rows(const void* x, const int* order, int div, const float* scale, void* out,
+                                    int n_rows, int hidden, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NF_REQUIRE(div > 0 && hidden > 0, "scale_gather_rows: bad sizes");
+  if (dtype == kF32)
+    launch_chained(scale_gather_rows_kernel<float>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, order, div, scale, (float*)out, hidden, n_rows);
+  else
+    launch_chained(scale_gather_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, (const __nv_bfloat16*)x, order, div, scale, (__nv_bfloat16*)out, hidden, n_rows);
+  return check_launch("scale_gather_rows");
+}

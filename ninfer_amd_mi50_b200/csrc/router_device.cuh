@@ -43,7 +43,9 @@ __device__ __forceinline__ float lane_dot(const float* __restrict__ xs, const fl
 }
 
 // One warp, one token: softmax over the E router logits, the k largest (ties to the lower
-// index), weights p_e or p_e / sum(selected).  `lg` is E floats of the warp's shared memory;
+// index), weights p_e or p_e / sum(selected).  `norm_topk` is a set of flags: bit 0 divides the
+// selected weights by their sum; bit 1 scores every expert by the sigmoid of its own logit
+// instead of the softmax over all (the selection and the weights then use those scores).  `lg` is E floats of the warp's shared memory;
 // logits[t, e] sits at row[e * exp_stride].
 // GLOBAL: the logits are in global memory, written by other blocks of this launch (read past
 // L1); otherwise they are in this block's shared memory.  `chosen`, if given, also receives the
@@ -54,6 +56,8 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
                                              int extra, int k, int norm_topk, int* __restrict__ topk_idx,
                                              float* __restrict__ topk_w, float* __restrict__ extra_out,
                                              int lane, unsigned short* chosen = nullptr) {
+  const bool sigmoid_scores = (norm_topk & 2) != 0;
+  norm_topk &= 1;
   // (the further rows' logits are asked for together with the experts', and stored once those are in)
   const bool has_extra = extra_out && lane < extra;
   float extra_v = 0.f;
@@ -82,12 +86,13 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
   bool bad = false;
   float sum = 0.f;
   for (int e = lane; e < E; e += 32) {
-    float p = expf(lg[e] - mx);
+    float p = sigmoid_scores ? 1.f / (1.f + expf(-lg[e])) : expf(lg[e] - mx);
     if (!(p >= 0.f && p <= 1.f)) { p = 0.f; bad = true; }
     lg[e] = p;
     sum += p;
   }
   sum = warp_sum(sum);
+  if (sigmoid_scores) sum = 1.f;                     // a score is its own weight
   bad = __any_sync(0xffffffffu, bad) || !(sum > 0.f);
   if (bad) sum = 1.f;
   __syncwarp();

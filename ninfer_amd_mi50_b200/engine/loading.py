@@ -46,7 +46,7 @@ def load_runner(model_dir: Optional[str] = None, *, config: Optional[Dict[str, A
                               gen_device=device if device.type == "cuda" else "cpu")
     else:
         source = CheckpointSource(model_dir)
-    log.info(f"loading {config.get('architectures', ['?'])[0]} as {options.dtype} on {device}")
+    log.info(f"loading {architecture_of(config).name} as {options.dtype} on {device}")
     load_model(model, source, dtype, device)
     source.close()
     cache = CacheManager(model.cache_specs(), model.state_specs(), page_size=options.page_size,

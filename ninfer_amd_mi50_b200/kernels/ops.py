@@ -551,8 +551,16 @@ def split_router(w_router: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.T
     return hi, lo
 
 
+def _route_flags(norm_topk: bool, scoring: str) -> int:
+    """The selection's flags: bit 0 divides the chosen weights by their sum, bit 1 scores an expert
+    by the sigmoid of its own logit instead of the softmax over all."""
+    if scoring not in ("softmax", "sigmoid"):
+        raise ValueError(f"router scoring {scoring!r}: 'softmax' or 'sigmoid'")
+    return (1 if norm_topk else 0) | (2 if scoring == "sigmoid" else 0)
+
+
 def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool,
-                split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None
+                split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None, scoring: str = "softmax"
                 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """Router logits (float32), softmax, top-k.  Rows of `w_router` beyond E give raw
     logits back (`extra`, [T, rows - E]).  Returns (idx int32 [T, k], weights float32 [T, k], extra).
@@ -578,11 +586,11 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_to
             _skinny(split[1], H, x, 0, low, rows, T, H, 1, rows, None, None, 1, False)
             logits_t += low
         _lib.call("nf_router_select", _p(logits_t), c_longlong(1), c_longlong(T), c_int(T), c_int(E),
-                  c_int(extra), c_int(k), c_int(1 if norm_topk else 0), _p(idx), _p(wts), _p(ext), _stream())
+                  c_int(extra), c_int(k), c_int(_route_flags(norm_topk, scoring)), _p(idx), _p(wts), _p(ext), _stream())
         return idx, wts, ext
     logits = torch.empty((T, E + extra), dtype=torch.float32, device=x.device)
     _lib.call("nf_router_topk", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra),
-              c_int(k), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext),
+              c_int(k), c_int(_route_flags(norm_topk, scoring)), _p(logits), _p(idx), _p(wts), _p(ext),
               c_int(_dt(x)), _stream())
     return idx, wts, ext
 
@@ -605,7 +613,7 @@ _TICKETS = {}
 
 
 def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool,
-          split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None):
+          split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None, scoring: str = "softmax"):
     """Routing of a step: `router_topk` and `moe_plan` together -> (idx, weights, extra, plan).
 
     Up to `TUNING["router_fused_max_rows"]` rows this is one launch: blocks compute the
@@ -613,7 +621,7 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
     _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
     T, H = x.shape
     if T == 0 or T > TUNING["router_fused_max_rows"]:
-        idx, wts, ext = router_topk(x, w_router, E, k, norm_topk, split=split)
+        idx, wts, ext = router_topk(x, w_router, E, k, norm_topk, split=split, scoring=scoring)
         return idx, wts, ext, moe_plan(idx, E)
     dev = x.device
     extra = w_router.shape[0] - E
@@ -629,14 +637,14 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
             and _lib.load().nf_router_cluster_fits(T, H, E, extra, k)):
         # one thread-block cluster: logits meet selection and plan in distributed shared memory
         _lib.call("nf_router_cluster", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra), c_int(k),
-                  c_int(1 if norm_topk else 0), None, _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
+                  c_int(_route_flags(norm_topk, scoring)), None, _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
                   _p(inv), _p(active), c_int(active.numel()), c_int(_dt(x)), _stream())
         return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
     key = str(dev)
     if key not in _TICKETS:
         _TICKETS[key] = torch.zeros((1,), dtype=torch.int32, device=dev)
     _lib.call("nf_router_fused", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra), c_int(k),
-              c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
+              c_int(_route_flags(norm_topk, scoring)), _p(logits), _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
               _p(inv), _p(active), c_int(active.numel()), _p(_TICKETS[key]), c_int(_dt(x)), _stream())
     return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
 
@@ -657,13 +665,22 @@ def moe_gather(x: torch.Tensor, plan: MoePlan, k: int) -> torch.Tensor:
     return xp
 
 
-def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
+def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[torch.Tensor] = None,
+              sorted_rows: bool = False) -> torch.Tensor:
     """Sorted pair p (token order[p] // k, expert e) -> silu(x Wgate_e^T) * (x Wup_e^T)  [T*k, I].
 
     `w13` is [E, 2I, H] (gate rows first), or `PackedWeights` of it for the bfloat16 kernels.
-    `gathered`: `moe_gather(x, plan, k)` if the caller has it already."""
+    `gathered`: `moe_gather(x, plan, k)` if the caller has it already.  `sorted_rows`: `x` itself
+    is [T*k, H] with row p belonging to sorted pair p (gathered, and possibly scaled, by the caller)."""
     _chk(x, "x")
-    T, H = x.shape
+    if sorted_rows:
+        T, H = plan.num_tokens, x.shape[1]
+        if x.shape[0] != T * k:
+            raise ValueError("moe_gemm1: sorted rows do not match the plan")
+        rows, div, gathered = None, 1, x
+    else:
+        T, H = x.shape
+        rows, div = plan.order, k
     packed = isinstance(w13, PackedWeights)
     if packed:
         E, inner = w13.groups, w13.n_features
@@ -678,8 +695,8 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[to
         return act
     if packed:
         if T <= TUNING["skinny_moe_max_tokens"]:
-            _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
-                    k, True, packed=True, group_map=plan.active)
+            _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, rows,
+                    div, True, packed=True, group_map=plan.active)
         else:
             # rows in sorted order, then one tensor-core launch over all experts
             xp = gathered if gathered is not None else moe_gather(x, plan, k)
@@ -688,11 +705,17 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[to
         return act
     path = "simt" if x.dtype == torch.float32 else _bf16_path(T, H, "bf16_moe")
     if path == "skinny":
-        _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True,
+        _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, rows, div, True,
                 group_map=plan.active)
     else:
-        _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
+        _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, rows, div, True)
     return act
+
+
+def moe_experts_sorted(xs: torch.Tensor, w13, w2, plan: MoePlan) -> torch.Tensor:
+    """Both products of the routed experts over rows that are already in the experts' order
+    (row p of `xs` is sorted pair p's input) -> [T*k, H] in the same order."""
+    return moe_gemm2(moe_gemm1(xs, w13, plan, plan.top_k, sorted_rows=True), w2, plan, plan_is_older=True)
 
 
 def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False) -> torch.Tensor:
@@ -915,6 +938,177 @@ def moe_combine_add_rmsnorm(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, s
     _lib.call("nf_moe_combine_add_rmsnorm", _p(y), _p(plan.inv), _p(wts), _p(shared), _p(gate),
               c_int(gate.shape[1] if gate is not None else 0), _p(h), _p(rows), _p(weight), c_float(eps),
               _p(out), c_int(T), c_int(R), c_int(h.shape[1]), c_int(k), _stream())
+
+
+# ---------------------------------------------------------------------------------------
+# layer norm, slices, gates
+# ---------------------------------------------------------------------------------------
+
+def add_layernorm(h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor],
+                  weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """h += delta (float32, in place); out = (h - mean) * rsqrt(var + eps) * weight, var the mean of
+    the squared deviations.  With `rows`: out[r] from h[rows[r]] + delta[rows[r]], h left alone."""
+    _chk(h, "h", torch.float32); _chk(weight, "weight", torch.float32); _chk(out, "out")
+    if delta is not None:
+        _chk(delta, "delta", out.dtype)
+    if rows is not None:
+        _chk(rows, "rows", torch.int32)
+    R = h.shape[0] if rows is None else rows.numel()
+    _lib.call("nf_add_layernorm", _p(h), _p(delta), _p(rows), _p(weight), c_float(eps), _p(out), c_int(R),
+              c_int(h.shape[1]), c_int(_dt(out)), _stream())
+
+
+def rms_norm_slice(x: torch.Tensor, col0: int, n: int, weight: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """Columns [col0, col0 + n) of x [T, ld] over their root mean square (eps inside the root),
+    times `weight` (float32 [n], or None) -> [T, n]."""
+    _chk(x, "x")
+    if weight is not None:
+        _chk(weight, "weight", torch.float32)
+    T, ld = x.shape
+    out = torch.empty((T, n), dtype=x.dtype, device=x.device)
+    _lib.call("nf_rms_norm_slice", _p(x), c_int(ld), c_int(col0), c_int(n), _p(weight), c_float(eps), _p(out),
+              c_int(n), c_int(T), c_int(_dt(x)), _stream())
+    return out
+
+
+def gated_group_rmsnorm(y: torch.Tensor, z_src: torch.Tensor, z_col0: int, weight: torch.Tensor, eps: float,
+                        parts: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """g = y * silu(z), z = z_src[:, z_col0 : z_col0 + inner]; every one of `parts` equal parts of
+    a row over its own root mean square; times weight -> [T, inner] in `out_dtype`.  y is float32."""
+    _chk(y, "y", torch.float32); _chk(z_src, "z_src", out_dtype); _chk(weight, "weight", torch.float32)
+    T, inner = y.shape
+    out = torch.empty((T, inner), dtype=out_dtype, device=y.device)
+    _lib.call("nf_gated_group_rmsnorm", _p(y), _p(z_src), c_int(z_src.shape[1]), c_int(z_col0), _p(weight),
+              c_float(eps), _p(out), c_int(T), c_int(inner), c_int(parts), c_int(_dt(out)), _stream())
+    return out
+
+
+def add_row_vector(h: torch.Tensor, vec: torch.Tensor) -> None:
+    """h[t] += vec for every row (float32, in place)."""
+    _chk(h, "h", torch.float32); _chk(vec, "vec", torch.float32)
+    if vec.numel() != h.shape[1]:
+        raise ValueError("add_row_vector: the vector does not have the rows' width")
+    _lib.call("nf_add_row_vector", _p(h), _p(vec), c_int(h.shape[0]), c_int(h.shape[1]), _stream())
+
+
+def heads_sigmoid_gate(v: torch.Tensor, g_src: torch.Tensor, g_col0: int) -> torch.Tensor:
+    """v [heads, T, n] (head-major) times sigmoid(g_src[:, g_col0 + head * n + i]) -> [T, heads * n]."""
+    _chk(v, "v"); _chk(g_src, "g_src", v.dtype)
+    heads, T, n = v.shape
+    out = torch.empty((T, heads * n), dtype=v.dtype, device=v.device)
+    _lib.call("nf_heads_sigmoid_gate", _p(v), _p(g_src), c_int(g_src.shape[1]), c_int(g_col0), _p(out), c_int(T),
+              c_int(heads), c_int(n), c_int(_dt(v)), _stream())
+    return out
+
+
+def scale_gather_rows(x: torch.Tensor, plan: "MoePlan", k: int, wts: torch.Tensor) -> torch.Tensor:
+    """Row p of the result is wts[pair] * x[pair // k], pair = plan.order[p]: the tokens in the
+    experts' order, each already multiplied by the weight of its (token, choice) pair."""
+    _chk(x, "x"); _chk(wts, "wts", torch.float32)
+    T, H = x.shape
+    out = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
+    _lib.call("nf_scale_gather_rows", _p(x), _p(plan.order), c_int(k), _p(wts), _p(out), c_int(T * k), c_int(H),
+              c_int(_dt(x)), _stream())
+    return out
+
+
+def heads_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [heads, T, a] times w [heads, a, b] -> [heads, T, b]: one product a head (a library's
+    batched product; float32 operands are multiplied in true float32)."""
+    _chk(x, "x", contiguous=False); _chk(w, "w", x.dtype, contiguous=False)
+    return torch.bmm(x, w)
+
+
+# ---------------------------------------------------------------------------------------
+# state-space mixer
+# ---------------------------------------------------------------------------------------
+
+CONV_MAX_TAPS = 8
+SCAN_MAX_STATE = 256
+
+
+def causal_conv_silu(src: torch.Tensor, col0: int, C: int, taps: torch.Tensor, bias: Optional[torch.Tensor],
+                     state: torch.Tensor, ctx) -> torch.Tensor:
+    """silu(bias + causal convolution per channel) of columns [col0, col0 + C) of src [T, ld] -> [T, C].
+    taps float32 [C, K] (last column: the current token).  `state` float32 [slots, >= (K - 1) * C]:
+    each request's last K - 1 inputs, read for the positions before this step and replaced by
+    the step's last inputs afterwards."""
+    _chk(src, "src"); _chk(taps, "taps", torch.float32); _chk(state, "state", torch.float32)
+    T, ld = src.shape
+    K = taps.shape[1]
+    out = torch.empty((T, C), dtype=src.dtype, device=src.device)
+    _lib.call("nf_causal_conv_silu", _p(src), c_int(ld), c_int(col0), c_int(C), _p(taps), _p(bias), c_int(K),
+              _p(state), c_longlong(state.stride(0)), _p(ctx.row_seg), _p(ctx.seg_row0), _p(ctx.seg_slot), _p(out),
+              c_int(T), c_int(ctx.S), c_int(_dt(src)), _stream())
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, x_col0: int, b_col0: int, c_col0: int, dt_src: torch.Tensor, dt_col0: int,
+             dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, state_off: int,
+             ctx, heads: int, P: int, N: int, groups: int) -> torch.Tensor:
+    """The selective scan of a step's rows, request by request, from and into each request's
+    state (float32 [slots, ...], the [heads, P, N] block starting at element `state_off`):
+    S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, dt = softplus(raw + dt_bias).
+    x, B, C are columns of `xbc`, raw dt a column of `dt_src`.  Returns y float32 [T, heads * P]."""
+    _chk(xbc, "xbc"); _chk(dt_src, "dt_src", xbc.dtype); _chk(state, "state", torch.float32)
+    for t, n in ((dt_bias, "dt_bias"), (A_log, "A_log"), (D, "D")):
+        _chk(t, n, torch.float32)
+    T = xbc.shape[0]
+    y = torch.empty((T, heads * P), dtype=torch.float32, device=xbc.device)
+    _lib.call("nf_ssd_scan", _p(xbc), c_int(xbc.shape[1]), c_int(x_col0), c_int(b_col0), c_int(c_col0), _p(dt_src),
+              c_int(dt_src.shape[1]), c_int(dt_col0), _p(dt_bias), _p(A_log), _p(D),
+              c_void_p(state.data_ptr() + 4 * state_off), c_longlong(state.stride(0)), _p(ctx.seg_row0),
+              _p(ctx.seg_slot), _p(y), c_int(ctx.S), c_int(heads), c_int(P), c_int(N), c_int(groups),
+              c_int(_dt(xbc)), _stream())
+    return y
+
+
+# ---------------------------------------------------------------------------------------
+# attention over latent rows
+# ---------------------------------------------------------------------------------------
+
+LATENT_MAX_RANK = 512
+
+
+def latent_append(src: torch.Tensor, col0: int, R: int, Dr: int, weight: torch.Tensor, eps: float,
+                  inv_freq: Optional[torch.Tensor], rot_dims: int, ctx, pages: torch.Tensor,
+                  block_table: torch.Tensor, page_size: int) -> None:
+    """Columns [col0, col0 + R + Dr) of src -> the cache row of each row's (request, position):
+    the first R over their root mean square times `weight`, the last Dr with their first
+    `rot_dims` turned by the position (half-split pairs)."""
+    _chk(src, "src"); _chk(pages, "pages", src.dtype); _chk(weight, "weight", torch.float32)
+    _chk(block_table, "block_table", torch.int32)
+    _lib.call("nf_latent_append", _p(src), c_int(src.shape[1]), c_int(col0), c_int(R), c_int(Dr), _p(weight),
+              c_float(eps), _p(inv_freq), c_int(rot_dims if inv_freq is not None else 0), _p(ctx.positions),
+              _p(ctx.row_seg), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(page_size),
+              c_int(pages.shape[0]), c_int(src.shape[0]), c_int(_dt(src)), _stream())
+
+
+def rope_head_slices(q: torch.Tensor, heads: int, head_stride: int, off: int, rot_dims: int,
+                     inv_freq: torch.Tensor, positions: torch.Tensor) -> None:
+    """In place: the slice [off, off + rot_dims) of every head of q [T, heads * head_stride] is turned."""
+    _chk(q, "q"); _chk(inv_freq, "inv_freq", torch.float32); _chk(positions, "positions", torch.int32)
+    _lib.call("nf_rope_head_slices", _p(q), c_int(q.shape[1]), c_int(heads), c_int(head_stride), c_int(off),
+              c_int(rot_dims), _p(inv_freq), _p(positions), c_int(q.shape[0]), c_int(_dt(q)), _stream())
+
+
+def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, head_stride: int, rot_off: int, Dr: int,
+                     pages: torch.Tensor, block_table: torch.Tensor, page_size: int, ctx, sink: Optional[torch.Tensor],
+                     scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of every head over the cached latent rows [c | k_rot]:
+    score = (q_abs[h] . c + q_rot[h] . k_rot) * scale, softmax whose denominator also holds
+    exp(sink[h]), result sum_j p_j c_j.  q_abs [heads, T, R]; q_rot is read from q [T, ld] at
+    head * head_stride + rot_off.  Returns [heads, T, R]."""
+    _chk(q_abs, "q_abs"); _chk(q, "q", q_abs.dtype); _chk(pages, "pages", q_abs.dtype)
+    heads, T, R = q_abs.shape
+    if sink is not None:
+        _chk(sink, "sink", torch.float32)
+    out = torch.empty((heads, T, R), dtype=q_abs.dtype, device=q_abs.device)
+    _lib.call("nf_latent_attention_generic", _p(q_abs), _p(q), c_int(q.shape[1]), c_int(head_stride), c_int(rot_off),
+              _p(pages), _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(sink),
+              _p(out), c_int(T), c_int(heads), c_int(R), c_int(Dr), c_int(page_size), c_int(pages.shape[0]),
+              c_int(window), c_float(scale), c_int(_dt(q_abs)), _stream())
+    return out
 
 
 # ---------------------------------------------------------------------------------------

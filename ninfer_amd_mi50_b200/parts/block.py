@@ -4,7 +4,7 @@ Pre-norm, as the reference runs a layer (src/models/model.hip:206-444):
 ``x1 = norm1(h)`` -> mixer -> ``h += o`` fused with ``x2 = norm2(h)`` (model.hip:311) ->
 feed-forward -> ``h += ffn``.  The last sum is left pending so that it fuses with the next
 block's first norm, which is what the reference's ``fused_residual_rmsnorm`` does one
-stage earlier.
+stage earlier.  A layer whose feed-forward is ``"none"`` is ``h += mixer(norm1(h))`` alone.
 """
 
 from __future__ import annotations
@@ -23,6 +23,8 @@ class PreNormBlock(Block):
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
 
     def parts(self):
+        if getattr(self.feed_forward, "absent", False):
+            return (self.norm1, self.mixer)             # no feed-forward: no second norm either
         return (self.norm1, self.mixer, self.norm2, self.feed_forward)
 
     @property
@@ -50,5 +52,7 @@ class PreNormBlock(Block):
             pending = summed(pending)
         x1 = self.norm1.add_norm(h, pending, ctx.dtype)
         a = self.mixer.forward(x1, ctx, cache, state)
+        if getattr(self.feed_forward, "absent", False):
+            return a                                    # the mixer's output is what is left pending
         x2 = self.norm2.add_norm(h, a, ctx.dtype)
         return self.feed_forward.forward(x2, ctx)

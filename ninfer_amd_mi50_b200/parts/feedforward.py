@@ -36,6 +36,19 @@ def _side_stream(device: torch.device, urgent: bool = False) -> "torch.cuda.Stre
     return _SIDE_STREAMS[key]
 
 
+@register_part("feed_forward", "none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: the block then ends with its mixer (and has no second norm)."""
+    graph_safe = True
+    absent = True
+
+    def __init__(self, prefix: str = ""):
+        self.prefix = prefix
+
+    def forward(self, x: torch.Tensor, ctx: StepContext):
+        raise RuntimeError("a layer without a feed-forward has nothing to run")
+
+
 @register_part("feed_forward", "dense_swiglu")
 class DenseSwiglu(FeedForward):
     graph_safe = True
@@ -71,10 +84,22 @@ class SparseMoeSwiglu(FeedForward):
     # set to a list to collect each call's selected experts (measurement only)
     record_routing = None
 
+    # tensor names below the prefix; `{e}` is the expert's number
+    DEFAULT_NAMES = (("router", "gate.weight"), ("gate", "experts.{e}.gate_proj.weight"),
+                     ("up", "experts.{e}.up_proj.weight"), ("down", "experts.{e}.down_proj.weight"))
+
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, norm_topk_prob: bool,
-                 moe_intermediate_size: int, shared_intermediate_size: int, prefix: str):
+                 moe_intermediate_size: int, shared_intermediate_size: int, prefix: str,
+                 scoring: str = "softmax", weight_on: str = "output", tensor_names=None):
         if not 1 <= top_k <= num_experts:
             raise ValueError(f"top_k={top_k} must lie in [1, num_experts={num_experts}]")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"scoring {scoring!r}: 'softmax' or 'sigmoid'")
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"weight_on {weight_on!r}: 'output' or 'input'")
+        self.scoring, self.weight_on = scoring, weight_on
+        self.names = dict(self.DEFAULT_NAMES)
+        self.names.update(dict(tensor_names or ()))
         kernels.check_router_sizes(num_experts, top_k)
         self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.norm_topk_prob = bool(norm_topk_prob)
@@ -88,14 +113,21 @@ class SparseMoeSwiglu(FeedForward):
     def has_shared(self) -> bool:
         return self.shared_intermediate_size > 0
 
+    def _n(self, what: str, e: int = 0) -> str:
+        return self.prefix + self.names[what].format(e=e)
+
+    @property
+    def plain_routed(self) -> bool:
+        """The usual routed sum: softmax scores, weights on the experts' outputs."""
+        return self.scoring == "softmax" and self.weight_on == "output"
+
     def tensor_specs(self) -> List[TensorSpec]:
         p, H, I, Is = self.prefix, self.hidden_size, self.moe_intermediate_size, self.shared_intermediate_size
-        specs = [TensorSpec(p + "gate.weight", (self.num_experts, H), role="router")]
+        specs = [TensorSpec(self._n("router"), (self.num_experts, H), role="router")]
         for e in range(self.num_experts):
-            q = f"{p}experts.{e}."
-            specs += [TensorSpec(q + "gate_proj.weight", (I, H)),
-                      TensorSpec(q + "up_proj.weight", (I, H)),
-                      TensorSpec(q + "down_proj.weight", (H, I))]
+            specs += [TensorSpec(self._n("gate", e), (I, H)),
+                      TensorSpec(self._n("up", e), (I, H)),
+                      TensorSpec(self._n("down", e), (H, I))]
         if self.has_shared:
             q = p + "shared_expert."
             specs += [TensorSpec(q + "gate_proj.weight", (Is, H)),
@@ -106,20 +138,19 @@ class SparseMoeSwiglu(FeedForward):
 
     def load(self, fetch: Fetch) -> None:
         p, H, I, E = self.prefix, self.hidden_size, self.moe_intermediate_size, self.num_experts
-        router = fetch(p + "gate.weight")
+        router = fetch(self._n("router"))
         if self.has_shared:
             # one matrix yields the router logits and the shared expert's gate logit
             router = torch.cat([router, fetch(p + "shared_expert_gate.weight")], dim=0)
         self.w_router = router.contiguous()
         self.w_router_split = kernels.split_router(self.w_router) if self.w_router.is_cuda else None
-        first = fetch(f"{p}experts.0.gate_proj.weight")
+        first = fetch(self._n("gate", 0))
         self.w13 = torch.empty((E, 2 * I, H), dtype=first.dtype, device=first.device)
         self.w2 = torch.empty((E, H, I), dtype=first.dtype, device=first.device)
         for e in range(E):
-            q = f"{p}experts.{e}."
-            self.w13[e, :I].copy_(first if e == 0 else fetch(q + "gate_proj.weight"))
-            self.w13[e, I:].copy_(fetch(q + "up_proj.weight"))
-            self.w2[e].copy_(fetch(q + "down_proj.weight"))
+            self.w13[e, :I].copy_(first if e == 0 else fetch(self._n("gate", e)))
+            self.w13[e, I:].copy_(fetch(self._n("up", e)))
+            self.w2[e].copy_(fetch(self._n("down", e)))
         del first
         if (self.w13.is_cuda and self.w13.dtype == torch.bfloat16 and kernels.can_pack(I, H)
                 and kernels.can_pack(H, I)):
@@ -136,7 +167,7 @@ class SparseMoeSwiglu(FeedForward):
             # keep the row-major form for the library's products)
             self.ws_packed = None
             if (isinstance(self.w13, kernels.PackedWeights) and kernels.TUNING["moe_stream_shared"]
-                    and self.ws13.dtype == torch.bfloat16):
+                    and self.ws13.dtype == torch.bfloat16 and self.plain_routed):
                 self.ws_packed = kernels.pack_shared_expert(self.ws13, self.ws2.contiguous(), I)
 
     def weight_bytes(self) -> int:
@@ -163,6 +194,8 @@ class SparseMoeSwiglu(FeedForward):
         more rows - the routing on a second stream beside the shared expert's products.
         (Without a shared expert, or with the thresholds moved: one kernel after the other.)"""
         E, k = self.num_experts, self.top_k
+        if not self.plain_routed:
+            return self._forward_scored(x)
         if (self.ws_packed is not None and x.is_cuda
                 and kernels.can_route_and_run_experts(x, self.w_router, self.w13, self.w2, E, k, shared=self.ws_packed)):
             # a decode step: routing, the experts' products and the shared expert's are one persistent launch
@@ -234,4 +267,25 @@ class SparseMoeSwiglu(FeedForward):
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         # not added up here: the next norm does it inside its own kernel (`RoutedSum`); whoever
         # cannot calls `materialize()`, which is `kernels.moe_combine`
+        return RoutedSum(y, plan, wts, shared, gate, x.dtype)
+
+    def _forward_scored(self, x: torch.Tensor):
+        """The routed sum with sigmoid scores and/or the weight on the expert's input: routing
+        (one launch on small steps), then the tokens are gathered into the experts' order - and,
+        with the weight on the input, multiplied by their pair's weight in the same pass - and
+        both products run over the sorted rows.  The sum that is left pending then carries unit
+        weights."""
+        E, k = self.num_experts, self.top_k
+        idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
+                                             split=self.w_router_split, scoring=self.scoring)
+        if SparseMoeSwiglu.record_routing is not None:
+            SparseMoeSwiglu.record_routing.append(idx.clone())
+        if self.weight_on == "input":
+            y = kernels.moe_experts_sorted(kernels.scale_gather_rows(x, plan, k, wts), self.w13, self.w2, plan)
+            wts = torch.ones_like(wts)
+        else:
+            y = kernels.moe_experts(x, self.w13, self.w2, plan, k)
+        shared = None
+        if self.has_shared:
+            shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         return RoutedSum(y, plan, wts, shared, gate, x.dtype)

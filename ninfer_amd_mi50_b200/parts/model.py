@@ -33,9 +33,18 @@ class DecoderModel:
             self.blocks.append(part_class("block", spec.arrangement)(norm1, mixer, norm2, ffn))
         self.final_norm = build_part("norm", plan.final_norm, prefix=plan.final_norm_name)
         self.order: List[LayerCall] = list(plan.order)
+        vectors = dict(plan.stream_vectors)
         for call in self.order:
-            if not (0 <= call.layer < len(self.blocks) and 0 <= call.cache < len(self.blocks)):
+            if not (0 <= call.layer < len(self.blocks) and call.cache >= 0):
                 raise ValueError(f"execution order names a layer that does not exist: {call}")
+            if call.add_vector is not None and not (
+                    call.add_vector[0] in vectors and 0 <= call.add_vector[1] < vectors[call.add_vector[0]]):
+                raise ValueError(f"execution order adds a vector the plan does not have: {call}")
+        # cache and state slots: usually one per layer (slot i is layer i's); an order that gives a
+        # layer a slot of its own per call names more
+        self.num_cache_slots = max([len(self.blocks)] + [c.cache + 1 for c in self.order])
+        self.num_state_slots = max([len(self.blocks)] + [c.state_slot() + 1 for c in self.order])
+        self.vectors: Dict[str, torch.Tensor] = {}
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
@@ -46,6 +55,8 @@ class DecoderModel:
         for b in self.blocks:
             specs += b.tensor_specs()
         specs += self.final_norm.tensor_specs()
+        for name, rows in self.plan.stream_vectors:
+            specs.append(TensorSpec(name, (rows, H), role="vector"))
         if not self.plan.tie_word_embeddings:
             specs.append(TensorSpec(self.plan.head_name, (V, H)))
         return specs
@@ -55,14 +66,30 @@ class DecoderModel:
         for b in self.blocks:
             b.load(fetch)
         self.final_norm.load(fetch)
+        self.vectors = {name: fetch(name) for name, _ in self.plan.stream_vectors}
         self.head = self.embedding if self.plan.tie_word_embeddings else fetch(self.plan.head_name)
 
+    def _slot_specs(self, count: int, slot_of, spec_of, what: str) -> list:
+        specs: list = [None] * count
+        named = set()
+        for call in self.order:
+            slot, spec = slot_of(call), spec_of(self.blocks[call.layer])
+            if slot in named and specs[slot] != spec:
+                raise ValueError(f"{what} slot {slot} is shared by layers that keep different things")
+            named.add(slot)
+            specs[slot] = spec
+        for i, b in enumerate(self.blocks):          # a layer the order never names keeps its own slot
+            if i not in named:
+                specs[i] = spec_of(b)
+        return specs
+
     def cache_specs(self) -> List[Optional[CacheSpec]]:
-        """Slot i belongs to layer i; None if that layer keeps nothing in pages."""
-        return [b.cache_spec() for b in self.blocks]
+        """What each cache slot keeps in pages (None: nothing).  Slot i belongs to layer i unless
+        the order says otherwise."""
+        return self._slot_specs(self.num_cache_slots, lambda c: c.cache, lambda b: b.cache_spec(), "cache")
 
     def state_specs(self) -> List[Optional[StateSpec]]:
-        return [b.state_spec() for b in self.blocks]
+        return self._slot_specs(self.num_state_slots, lambda c: c.state_slot(), lambda b: b.state_spec(), "state")
 
     @property
     def graph_safe(self) -> bool:
@@ -75,6 +102,7 @@ class DecoderModel:
 
     def weight_bytes(self) -> int:
         n = sum(b.weight_bytes() for b in self.blocks) + self.final_norm.weight_bytes()
+        n += sum(v.numel() * 4 for v in self.vectors.values())
         return n + self.head.numel() * self.head.element_size()
 
     # ---- one pass over the step's rows --------------------------------------------------
@@ -86,12 +114,18 @@ class DecoderModel:
         kernels.embed_rows(self.embedding, ctx.token_ids, h)
         pending = None
         for call in self.order:
+            if call.add_vector is not None:
+                # (the pending contribution has not been added yet; the sums commute)
+                kernels.add_row_vector(h, self.vectors[call.add_vector[0]][call.add_vector[1]])
             pending = self.blocks[call.layer].forward(
-                h, pending, ctx, cache_view(call.cache, call.append), state_of(call.layer))
+                h, pending, ctx, cache_view(call.cache, call.append), state_of(call.state_slot()))
         R = ctx.logit_rows.numel()
         if R == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=ctx.device)
         if not self.final_norm.takes_unsummed:
             pending = summed(pending)
         x = self.final_norm.add_norm_rows(h, pending, ctx.logit_rows, ctx.dtype)
-        return kernels.linear(x, self.head, out_dtype=torch.float32)
+        logits = kernels.linear(x, self.head, out_dtype=torch.float32)
+        if self.plan.logit_scale != 1.0:
+            logits.mul_(self.plan.logit_scale)
+        return logits

@@ -58,3 +58,39 @@ class RmsNorm(Norm):
         else:
             kernels.add_rmsnorm_rows(h, summed(delta), rows, self.weight, self.eps, out)
         return out
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias, fused with the residual sum:
+    ``y = (x - mean(x)) / sqrt(var(x) + eps) * w`` with ``var`` the mean of the squared
+    deviations from the mean.  Sum, mean, variance and product are 32-bit in both modes."""
+
+    graph_safe = True
+
+    def __init__(self, size: int, eps: float, prefix: str, weight_name: str = "weight"):
+        self.size, self.eps, self.prefix, self.weight_name = int(size), float(eps), prefix, weight_name
+        self.weight: Optional[torch.Tensor] = None
+
+    def _name(self) -> str:
+        # a checkpoint may name the weight by the norm's own name ("<layer>.norm1"), without a suffix
+        return self.prefix + self.weight_name if self.weight_name else self.prefix.rstrip(".")
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self._name(), (self.size,), role="vector", init="norm")]
+
+    def load(self, fetch: Fetch) -> None:
+        self.weight = fetch(self._name())
+
+    def weight_bytes(self) -> int:
+        return self.size * 4
+
+    def add_norm(self, h, delta, out_dtype):
+        out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+        kernels.add_layernorm(h, summed(delta), None, self.weight, self.eps, out)
+        return out
+
+    def add_norm_rows(self, h, delta, rows, out_dtype):
+        out = torch.empty((rows.numel(), h.shape[1]), dtype=out_dtype, device=h.device)
+        kernels.add_layernorm(h, summed(delta), rows, self.weight, self.eps, out)
+        return out

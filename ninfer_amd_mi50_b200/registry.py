@@ -56,6 +56,8 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(config_dict: Dict[str, Any]) -> Architecture:
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]          # some configurations name it as one string
     if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a non-empty list of names; "
                           f"registered: {architecture_names()}")
