@@ -580,9 +580,14 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_to
         # weights.  Products of bfloat16 values are exact, sums are float32.
         rows = E + extra
         logits_t = torch.empty((rows, T), dtype=torch.float32, device=x.device)
+        # The streaming product asks for its weight operand before it waits for the kernel before
+        # it - and here that operand is `x`, which that kernel may still be writing.  So these
+        # launches are ordinary ones (chained, they read rows of x that were not written yet).
+        chain_break()
         _skinny(split[0], H, x, 0, logits_t, rows, T, H, 1, rows, None, None, 1, False)
         if split[1] is not None:
             low = torch.empty_like(logits_t)
+            chain_break()
             _skinny(split[1], H, x, 0, low, rows, T, H, 1, rows, None, None, 1, False)
             logits_t += low
         _lib.call("nf_router_select", _p(logits_t), c_longlong(1), c_longlong(T), c_int(T), c_int(E),
