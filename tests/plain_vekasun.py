@@ -175,18 +175,22 @@ def layer_runs(cfg: dict) -> List[tuple]:
     return runs + [(i, None) for i in range(b, n)]
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, residuals: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence; `residuals` collects x after every layer run."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, residuals: Optional[list] = None,
+            forced: Optional[Dict[int, torch.Tensor]] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence; `residuals` collects x after every layer run;
+    `forced` maps the number of a layer run to the experts [T, top] its feed-forward is to use
+    instead of its own choice (their weights are still this model's own scores)."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.as_tensor(list(tokens), dtype=torch.long)]
     loop = cfg.get("loop")
-    for i, t in layer_runs(cfg):
+    for run, (i, t) in enumerate(layer_runs(cfg)):
         if t is not None and i == int(loop["start"]):
             x = x + w["loop.step"][t][None, :]
         L, p = cfg["layers"][i], f"l{i}."
         x = x + MIXERS[L["type"]](layer_norm(x, w[p + "norm1"], eps), w, p + "mix.", L["mixer"], eps)
         if L.get("mlp") is not None:
-            x = x + moe_scaled_input(layer_norm(x, w[p + "norm2"], eps), w, p + "mlp.", L["mlp"])
+            x = x + moe_scaled_input(layer_norm(x, w[p + "norm2"], eps), w, p + "mlp.", L["mlp"],
+                                     None if forced is None else forced.get(run))
         if residuals is not None:
             residuals.append(x.clone())
     return lin(layer_norm(x, w["final.norm"], eps), w["head"]) * float(cfg["logit_scale"])
