@@ -132,21 +132,35 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ldx, int x_col0, int b_col0, int 
       dec[threadIdx.x] = expf(-rate * dt);
     }
     __syncthreads();
-    for (int tt = 0; tt < nc; ++tt) {
-      const float a = dec[tt], xv = xs[tt * kScanCols + pl];
-      const float dx = dts[tt] * xv;
-      float acc = 0.f;
+    // The recurrence over the chunk's tokens touches only registers and shared memory; each
+    // token's sum over N stays a per-lane partial until the chunk is done, so that the sixteen
+    // shuffle reductions are independent of one another and of the recurrence.
+    float acc[kScanChunk];
 #pragma unroll
-      for (int i = 0; i < NPER; ++i) {
-        const int n = i * kScanLanes + ln;
-        if (n < N) {
-          s[i] = fmaf(a, s[i], dx * Bs[tt * N + n]);
-          acc = fmaf(s[i], Cs[tt * N + n], acc);
+    for (int tt = 0; tt < kScanChunk; ++tt) {
+      acc[tt] = 0.f;
+      if (tt < nc) {
+        const float a = dec[tt];
+        const float dx = dts[tt] * xs[tt * kScanCols + pl];
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+          const int n = i * kScanLanes + ln;
+          if (n < N) {
+            s[i] = fmaf(a, s[i], dx * Bs[tt * N + n]);
+            acc[tt] = fmaf(s[i], Cs[tt * N + n], acc[tt]);
+          }
         }
       }
+    }
 #pragma unroll
-      for (int o = kScanLanes / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ln == 0) ys[tt * kScanCols + pl] = acc + skip * xv;
+    for (int tt = 0; tt < kScanChunk; ++tt) {
+#pragma unroll
+      for (int o = kScanLanes / 2; o > 0; o >>= 1) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
+    }
+    if (ln == 0) {
+#pragma unroll
+      for (int tt = 0; tt < kScanChunk; ++tt)
+        if (tt < nc) ys[tt * kScanCols + pl] = acc[tt] + skip * xs[tt * kScanCols + pl];
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nc * kScanCols; i += blockDim.x) {

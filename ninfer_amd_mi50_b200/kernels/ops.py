@@ -1073,6 +1073,8 @@ def ssd_scan(xbc: torch.Tensor, x_col0: int, b_col0: int, c_col0: int, dt_src: t
 # ---------------------------------------------------------------------------------------
 
 LATENT_MAX_RANK = 512
+LATENT_TILE_PAIRS = 32      # (token, head) pairs a tile of the tensor-core kernel
+LATENT_KEY_BLOCK = 64       # keys a block of that kernel
 
 
 def latent_append(src: torch.Tensor, col0: int, R: int, Dr: int, weight: torch.Tensor, eps: float,
@@ -1109,6 +1111,29 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, head_stride: int, rot
     if sink is not None:
         _chk(sink, "sink", torch.float32)
     out = torch.empty((heads, T, R), dtype=q_abs.dtype, device=q_abs.device)
+    if T == 0:
+        return out
+    if (q_abs.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic" and window == 0
+            and _lib.load().nf_latent_attention_mma_fits(c_int(R), c_int(Dr), c_int(head_stride), c_int(rot_off),
+                                                        c_int(q.shape[1]))):
+        # tensor cores: tiles of 32 (token, head) pairs, keys in blocks of 64, long contexts split
+        per_row = (heads + LATENT_TILE_PAIRS - 1) // LATENT_TILE_PAIRS
+        if getattr(ctx, "all_single", False) or getattr(ctx, "seg_len_host", None) is None:
+            tiles, n_tiles = None, ctx.S * per_row          # one row a segment: the kernel numbers the tiles itself
+        else:
+            tiles, n_tiles = ctx.pair_tiles(heads, LATENT_TILE_PAIRS)
+        n_blocks = max(1, (int(ctx.max_context) + LATENT_KEY_BLOCK - 1) // LATENT_KEY_BLOCK)
+        nsplit = min(n_blocks, max(1, (2 * 148 + n_tiles - 1) // n_tiles))
+        per_split = (n_blocks + nsplit - 1) // nsplit
+        nsplit = (n_blocks + per_split - 1) // per_split
+        ws_o = torch.empty((T * heads, nsplit, R), dtype=torch.float32, device=q_abs.device)
+        ws_ml = torch.empty((T * heads, nsplit, 2), dtype=torch.float32, device=q_abs.device)
+        _lib.call("nf_latent_attention_mma", _p(q_abs), _p(q), c_int(q.shape[1]), c_int(head_stride), c_int(rot_off),
+                  _p(pages), _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0),
+                  _p(tiles), c_int(n_tiles), _p(sink), _p(out), _p(ws_o), _p(ws_ml), c_int(T), c_int(heads), c_int(R),
+                  c_int(Dr), c_int(page_size), c_int(pages.shape[0]), c_float(scale), c_int(nsplit), c_int(per_split),
+                  _stream())
+        return out
     _lib.call("nf_latent_attention_generic", _p(q_abs), _p(q), c_int(q.shape[1]), c_int(head_stride), c_int(rot_off),
               _p(pages), _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(sink),
               _p(out), c_int(T), c_int(heads), c_int(R), c_int(Dr), c_int(page_size), c_int(pages.shape[0]),

@@ -158,6 +158,24 @@ class StepContext:
         return t, n_tiles
 
 
+    def pair_tiles(self, heads: int, pairs_per_tile: int) -> Tuple[torch.Tensor, int]:
+        """Tiles over the (row, head) pairs of every segment, `pairs_per_tile` consecutive pairs of
+        one segment each (pair = row within the segment * heads + head).  Returns (int32 [n, 2] of
+        (segment, first pair), n).  Built on the host; not available in graph mode."""
+        key = ("pair_tiles", heads, pairs_per_tile)
+        if key in self._tiles:
+            return self._tiles[key]
+        if self.seg_len_host is None:
+            raise RuntimeError("pair_tiles needs host segment lengths (not in graph mode)")
+        flat: List[int] = []
+        for s, n in enumerate(self.seg_len_host):
+            for p in range(0, n * heads, pairs_per_tile):
+                flat += [s, p]
+        n_tiles = len(flat) // 2
+        t = torch.tensor(flat, dtype=torch.int32).reshape(n_tiles, 2).to(self.device)
+        self._tiles[key] = (t, n_tiles)
+        return t, n_tiles
+
     def single_rows(self) -> Tuple[Optional[torch.Tensor], int]:
         """Rows of the segments that bring exactly one row (decoded tokens, or a prompt's last
         token arriving alone), as (int32 tensor on the device, count); (None, 0) if there are

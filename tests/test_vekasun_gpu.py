@@ -240,6 +240,41 @@ def test_latent_attention_alone_with_a_sink_that_matters(tmp_path, dtype, heads,
     assert (PV.forward(cfg, no_sink, toks) - want).abs().max() > 0.05 * want.abs().max()
 
 
+@pytest.mark.parametrize("heads,dim,rot_dim,dims,vdim,kv_rank,q_rank", [(3, 16, 16, 16, 24, 64, 40), (40, 8, 32, 16, 8, 128, 24),
+                                                                      (16, 32, 0, 0, 16, 192, 32), (5, 24, 48, 48, 32, 256, 48)])
+def test_latent_attention_on_tensor_cores(tmp_path, heads, dim, rot_dim, dims, vdim, kv_rank, q_rank):
+    """Latent widths that are multiples of 64 take the tensor-core kernel in bfloat16 (tiles of 32
+    (token, head) pairs, key blocks of 64, long contexts split and merged): whole, in portions that
+    end inside and on key blocks, token by token, and in a batch of unequal requests - against the
+    plain model, and against the engine's plain kernel."""
+    from ninfer_amd_mi50_b200 import kernels
+    from ninfer_amd_mi50_b200.engine import load_runner
+    assert kernels.lib.load().nf_latent_attention_mma_fits(kv_rank, rot_dim, dim + rot_dim, dim, heads * (dim + rot_dim))
+    mix = VC.attention(heads, dim, rot_dim, vdim, kv_rank, q_rank, 1.5 / math.sqrt(dim + rot_dim), 900.0, dims)
+    cfg = one_layer("latent_attention", mix, width=72)
+    rep = {"l0.mix.sink": torch.linspace(2.0, -3.0, heads)}
+    d = VC.write_folder(cfg, 70 + heads, str(tmp_path / "m"), replace=rep,
+                        scale={".mix.uq": 12.0, ".mix.uk": 8.0, ".mix.dkv": 4.0, ".mix.dq": 3.0, ".mix.g": 15.0, ".mix.uv": 5.0, ".mix.o": 5.0})
+    cfg, w = VC.read_folder(d)
+    toks = random_tokens(330, cfg["vocab"], 5)
+    want = PV.forward(cfg, w, toks)
+    for cuts in (None, [63, 1, 64, 2, 130, 70], [200] + [1] * 130):
+        got, _ = run_alone(cfg, d, toks, "bfloat16", cuts, max_context=384)
+        compare(got, want, "bfloat16", f"tensor-core latent attention cut {cuts and cuts[:3]}")
+    reqs = {f"r{i}": random_tokens(n, cfg["vocab"], 80 + i) for i, n in enumerate([129, 7, 64, 200])}
+    runner = load_runner(d, options=options("bfloat16", max_context=256))
+    got, _ = run(runner, schedules.mixed(reqs, max_live=4, page=16, tail=6))
+    kernels.TUNING["bf16_attention"] = "generic"
+    try:
+        plain, _ = run(runner, schedules.mixed(reqs, max_live=4, page=16, tail=6))
+    finally:
+        kernels.TUNING["bf16_attention"] = "auto"
+    for r, t in reqs.items():
+        ref = PV.forward(cfg, w, t)
+        compare(got[r], ref, "bfloat16", f"tensor-core latent attention, batch, {r}")
+        compare(plain[r], ref, "bfloat16", f"plain latent attention, batch, {r}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_one_far_key_among_hundreds_is_found_across_pages_and_portions(tmp_path, dtype):
     """In a one-layer model a token's query and key depend on the token alone (and, in the rotated
