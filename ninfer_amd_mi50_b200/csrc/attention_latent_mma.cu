@@ -9,7 +9,8 @@
 // which arrive in shared memory through a two-deep cp.async ring (rows of W + 8 elements, so
 // that ldmatrix meets no bank conflict):
 //   S = Q K^T   [32 x 64]: warp w owns the block's keys 8w .. 8w+7 over all W columns;
-//   row maxima and sums meet in shared memory; P (bfloat16) is written there;
+//   row maxima and sums meet in shared memory; P is written there as two bfloat16 halves (the
+//   rounding and its remainder), so that the weights keep 16 bits of mantissa;
 //   O += P C    [32 x R]:  warp w owns R / 8 output columns; C is the block's first R columns,
 //               read through ldmatrix.trans as the k-major operand.
 // Maxima, exponentials, sums and O are float32.  Long contexts are cut into `nsplit` runs of
@@ -58,8 +59,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, const __nv_
   const int W = R + Dr, WS = W + kLmPad;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lm_raw);              // [32][WS]
   __nv_bfloat16* Ks = Qs + kLmRows * WS;                                      // [2][64][WS]
-  __nv_bfloat16* Ps = Ks + 2 * kLmKeys * WS;                                  // [32][64 + 8]
-  float* smax = reinterpret_cast<float*>(Ps + kLmRows * (kLmKeys + kLmPad));  // [8][32]
+  __nv_bfloat16* Ps = Ks + 2 * kLmKeys * WS;                                  // [2][32][64 + 8]: leading and trailing half of P
+  float* smax = reinterpret_cast<float*>(Ps + 2 * kLmRows * (kLmKeys + kLmPad));  // [8][32]
   float* ssum = smax + 8 * kLmRows;                                           // [8][32]
   int* row_pos = reinterpret_cast<int*>(ssum + 8 * kLmRows);                  // [32]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -192,10 +193,15 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, const __nv_
       const float p0 = (s[mt][hi * 2] == -INFINITY) ? 0.f : __expf(s[mt][hi * 2] - m_new);
       const float p1 = (s[mt][hi * 2 + 1] == -INFINITY) ? 0.f : __expf(s[mt][hi * 2 + 1] - m_new);
       m_run[i] = m_new;
-      // the sum is taken over the rounded weights, which are what multiplies the values
+      // a weight goes to the tensor cores as two bfloat16 numbers, its rounding and what the rounding
+      // left (16 bits of mantissa together): with a single one, a row that rests on one far key
+      // carried three times the error of the plain kernel
       const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-      *reinterpret_cast<__nv_bfloat162*>(Ps + row * (kLmKeys + kLmPad) + warp * 8 + (lane & 3) * 2) = pb;
-      float sum = __bfloat162float(pb.x) + __bfloat162float(pb.y);
+      const __nv_bfloat162 pl = __floats2bfloat162_rn(p0 - __bfloat162float(pb.x), p1 - __bfloat162float(pb.y));
+      const int pofs = row * (kLmKeys + kLmPad) + warp * 8 + (lane & 3) * 2;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + pofs) = pb;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + kLmRows * (kLmKeys + kLmPad) + pofs) = pl;
+      float sum = p0 + p1;
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       if ((lane & 3) == 0) ssum[warp * kLmRows + row] = sum;
@@ -222,10 +228,12 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, const __nv_
       const unsigned ca = lm_smem(Kb + ((lane & 7) + ((lane >> 3) & 1) * 8) * WS + warp * (8 * NT) + (lane >> 4) * 8);
 #pragma unroll
       for (int ks = 0; ks < kLmKeys / 16; ++ks) {
-        unsigned a[2][4];
+        unsigned a[2][4], al[2][4];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+        for (int mt = 0; mt < 2; ++mt) {
           lm_ldm4(pa + (mt * 16 * (kLmKeys + kLmPad) + ks * 16) * 2, a[mt][0], a[mt][1], a[mt][2], a[mt][3]);
+          lm_ldm4(pa + ((kLmRows + mt * 16) * (kLmKeys + kLmPad) + ks * 16) * 2, al[mt][0], al[mt][1], al[mt][2], al[mt][3]);
+        }
 #pragma unroll
         for (int np = 0; np < NT; np += 2) {
           unsigned b0, b1, b2, b3;
@@ -233,7 +241,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, const __nv_
 #pragma unroll
           for (int mt = 0; mt < 2; ++mt) {
             lm_mma(o[mt][np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
-            if (np + 1 < NT) lm_mma(o[mt][np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+            lm_mma(o[mt][np], al[mt][0], al[mt][1], al[mt][2], al[mt][3], b0, b1);
+            if (np + 1 < NT) {
+              lm_mma(o[mt][np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+              lm_mma(o[mt][np + 1], al[mt][0], al[mt][1], al[mt][2], al[mt][3], b2, b3);
+            }
           }
         }
       }
@@ -287,7 +299,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ ws_o, co
 
 static size_t lm_smem_bytes(int R, int Dr) {
   const int WS = R + Dr + kLmPad;
-  return (size_t)(kLmRows + 2 * kLmKeys) * WS * 2 + (size_t)kLmRows * (kLmKeys + kLmPad) * 2 + 2 * 8 * kLmRows * 4 + kLmRows * 4;
+  return (size_t)(kLmRows + 2 * kLmKeys) * WS * 2 + (size_t)2 * kLmRows * (kLmKeys + kLmPad) * 2 + 2 * 8 * kLmRows * 4 + kLmRows * 4;
 }
 
 }  // namespace nf
