@@ -80,6 +80,8 @@ constexpr int kScanLanes = 16;     // lanes that share one column's N states
 constexpr int kScanCols = 8;       // columns of P a CTA owns
 constexpr int kScanChunk = 16;     // tokens staged at a time
 constexpr int kScanMaxPer = 16;    // N <= 256
+constexpr int kScanStage = 8;      // 16-byte loads a thread keeps in flight for the next chunk
+static_assert(kScanLanes * kScanCols == kScanChunk * kScanCols, "one thread stages one x of a chunk");
 
 template <typename T, int NPER>
 __global__ void __launch_bounds__(kScanLanes * kScanCols)
@@ -112,26 +114,80 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ldx, int x_col0, int b_col0, int 
     const int n = i * kScanLanes + ln;
     s[i] = (live && n < N) ? S[n] : 0.f;
   }
+  // Staging.  When the columns are 16-byte aligned, a chunk's B, C, x and dt are asked for (16 bytes a
+  // load, into registers) while the chunk before it is being worked on, and stored to shared memory
+  // once that is done; otherwise element by element at the chunk's start.
+  constexpr int VE = 16 / (int)sizeof(T);
+  const int vpr = N / VE;                                         // 16-byte pieces of one token's B (or C)
+  const bool vec = (N % VE == 0) && (ldx % VE == 0) && ((b_col0 + g * N) % VE == 0) && ((c_col0 + g * N) % VE == 0) &&
+                   (2 * kScanChunk * vpr <= kScanStage * (int)blockDim.x);
+  uint4 pre[kScanStage];
+  float pre_x = 0.f, pre_dt = 0.f;
+  auto issue = [&](int c0) {
+    const int nc = min(kScanChunk, n_rows - c0);
+#pragma unroll
+    for (int k = 0; k < kScanStage; ++k) {
+      const int idx = threadIdx.x + k * blockDim.x;
+      const int tt = idx / (2 * vpr), rest = idx - tt * 2 * vpr;
+      if (tt < nc) {
+        const int col = (rest < vpr ? b_col0 : c_col0) + g * N + (rest < vpr ? rest : rest - vpr) * VE;
+        pre[k] = *reinterpret_cast<const uint4*>(xbc + (size_t)(r0 + c0 + tt) * ldx + col);
+      }
+    }
+    {
+      const int tt = threadIdx.x / kScanCols, pp = threadIdx.x - tt * kScanCols;
+      pre_x = (tt < nc && p0 + pp < P) ? to_float(xbc[(size_t)(r0 + c0 + tt) * ldx + x_col0 + h * P + p0 + pp]) : 0.f;
+    }
+    if (threadIdx.x < nc) pre_dt = to_float(dt_src[(size_t)(r0 + c0 + threadIdx.x) * ld_dt + dt_col0 + h]);
+  };
+  if (vec && n_rows > 0) issue(0);
   for (int c0 = 0; c0 < n_rows; c0 += kScanChunk) {
     const int nc = min(kScanChunk, n_rows - c0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nc * N; i += blockDim.x) {
-      const int tt = i / N, n = i - tt * N;
-      const T* row = xbc + (size_t)(r0 + c0 + tt) * ldx;
-      Bs[tt * N + n] = to_float(row[b_col0 + g * N + n]);
-      Cs[tt * N + n] = to_float(row[c_col0 + g * N + n]);
-    }
-    for (int i = threadIdx.x; i < nc * kScanCols; i += blockDim.x) {
-      const int tt = i / kScanCols, pp = i - tt * kScanCols;
-      xs[i] = p0 + pp < P ? to_float(xbc[(size_t)(r0 + c0 + tt) * ldx + x_col0 + h * P + p0 + pp]) : 0.f;
-    }
-    if (threadIdx.x < nc) {
-      const float v = to_float(dt_src[(size_t)(r0 + c0 + threadIdx.x) * ld_dt + dt_col0 + h]) + bias;
-      const float dt = v > 20.f ? v : log1pf(expf(v));
-      dts[threadIdx.x] = dt;
-      dec[threadIdx.x] = expf(-rate * dt);
+    if (vec) {
+#pragma unroll
+      for (int k = 0; k < kScanStage; ++k) {
+        const int idx = threadIdx.x + k * blockDim.x;
+        const int tt = idx / (2 * vpr), rest = idx - tt * 2 * vpr;
+        if (tt < nc) {
+          float* dst = (rest < vpr ? Bs : Cs) + tt * N + (rest < vpr ? rest : rest - vpr) * VE;
+          if (sizeof(T) == 2) {
+            float f[8];
+            unpack8(pre[k], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[e] = f[e];
+          } else {
+            *reinterpret_cast<uint4*>(dst) = pre[k];
+          }
+        }
+      }
+      xs[threadIdx.x] = pre_x;                                   // blockDim == chunk * cols
+      if (threadIdx.x < nc) {
+        const float v = pre_dt + bias;
+        const float dt = v > 20.f ? v : log1pf(expf(v));
+        dts[threadIdx.x] = dt;
+        dec[threadIdx.x] = expf(-rate * dt);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nc * N; i += blockDim.x) {
+        const int tt = i / N, n = i - tt * N;
+        const T* row = xbc + (size_t)(r0 + c0 + tt) * ldx;
+        Bs[tt * N + n] = to_float(row[b_col0 + g * N + n]);
+        Cs[tt * N + n] = to_float(row[c_col0 + g * N + n]);
+      }
+      for (int i = threadIdx.x; i < nc * kScanCols; i += blockDim.x) {
+        const int tt = i / kScanCols, pp = i - tt * kScanCols;
+        xs[i] = p0 + pp < P ? to_float(xbc[(size_t)(r0 + c0 + tt) * ldx + x_col0 + h * P + p0 + pp]) : 0.f;
+      }
+      if (threadIdx.x < nc) {
+        const float v = to_float(dt_src[(size_t)(r0 + c0 + threadIdx.x) * ld_dt + dt_col0 + h]) + bias;
+        const float dt = v > 20.f ? v : log1pf(expf(v));
+        dts[threadIdx.x] = dt;
+        dec[threadIdx.x] = expf(-rate * dt);
+      }
     }
     __syncthreads();
+    if (vec && c0 + kScanChunk < n_rows) issue(c0 + kScanChunk);   // in flight while this chunk is worked on
     // The recurrence over the chunk's tokens touches only registers and shared memory; each
     // token's sum over N stays a per-lane partial until the chunk is done, so that the sixteen
     // shuffle reductions are independent of one another and of the recurrence.

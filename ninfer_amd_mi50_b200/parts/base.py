@@ -167,10 +167,16 @@ class StepContext:
             return self._tiles[key]
         if self.seg_len_host is None:
             raise RuntimeError("pair_tiles needs host segment lengths (not in graph mode)")
-        flat: List[int] = []
+        # heaviest first (a tile late in a long prompt reads many more keys than an early one): the
+        # device hands CTAs to SMs as they fall free, so the light tiles fill the end
+        found = []
+        pos0 = self.seg_pos0_host or [0] * len(self.seg_len_host)
         for s, n in enumerate(self.seg_len_host):
             for p in range(0, n * heads, pairs_per_tile):
-                flat += [s, p]
+                last_row = min(n * heads, p + pairs_per_tile) - 1
+                found.append((-(pos0[s] + last_row // heads), s, p))
+        found.sort()
+        flat: List[int] = [v for _, s, p in found for v in (s, p)]
         n_tiles = len(flat) // 2
         t = torch.tensor(flat, dtype=torch.int32).reshape(n_tiles, 2).to(self.device)
         self._tiles[key] = (t, n_tiles)
