@@ -95,7 +95,7 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
         # pairs: sum over rows of the keys each sees; rows_ctx: cache tokens that must be read once
         return {
             "nf_latent_attention_generic": (rows_ctx * Wl * 2 + 2 * T * H * R * 2, 2.0 * H * (Wl + R) * pairs),
-            "nf_latent_attention": (rows_ctx * Wl * 2 + 2 * T * H * R * 2, 2.0 * H * (Wl + R) * pairs),
+            "nf_latent_attention_mma": (rows_ctx * Wl * 2 + 2 * T * H * R * 2, 2.0 * H * (Wl + R) * pairs),
             "nf_prefill_attention_tc": (rows_ctx * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs),
             "nf_prefill_attention": (rows_ctx * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs),
             "nf_decode_attention": (rows_ctx * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs),

@@ -55,7 +55,17 @@ ONE_PASS = {
     ],
 }
 
-CONFIGS = {"looped": (LOOPED, 21), "straight": (STRAIGHT, 22), "one_pass": (ONE_PASS, 23)}
+# nothing a multiple of 8: the 16-byte-row kernels must step aside for the general ones
+AWKWARD = {
+    "architecture": "Vekasun", "vocab": 97, "width": 100, "norm": {"eps": 2e-5}, "logit_scale": 3.0,
+    "loop": {"start": 1, "stop": 2, "times": 2},
+    "layers": [
+        {"type": "latent_attention", "mixer": attention(2, 12, 6, 10, 20, 28, 0.3, 100.0, 6), "mlp": moe(36, 3, 2)},
+        {"type": "mamba2", "mixer": state_space(3, 10, 12, 3, 4, 3), "mlp": moe(20, 5, 1)},
+    ],
+}
+
+CONFIGS = {"looped": (LOOPED, 21), "straight": (STRAIGHT, 22), "one_pass": (ONE_PASS, 23), "awkward": (AWKWARD, 24)}
 
 
 def write_folder(config, seed, out_dir, replace=None, scale=None):
