@@ -13,15 +13,19 @@ namespace nf {
 
 // h[t] += delta[t] (if delta); out[t] = (h[t] - mean) * rsqrt(var + eps) * w.
 // With `rows`, row r reads h[rows[r]] / delta[rows[r]], writes out[r] and leaves h alone.
+// With `y`, delta[t] is the routed experts' sum that was left pending,
+// sum_j wts[t, j] * y[inv[t * k + j]] (j ascending; wts null: unit weights), rounded to T as the
+// separate combine kernel rounds it, so both ways give the same bits.
 template <typename T, bool GATHER>
 __global__ void add_layernorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
                                      const int* __restrict__ rows, const float* __restrict__ w,
-                                     float eps, T* __restrict__ out, int hidden) {
+                                     float eps, T* __restrict__ out, int hidden, const T* __restrict__ y,
+                                     const int* __restrict__ inv, const float* __restrict__ wts, int k) {
   extern __shared__ float row[];      // [hidden]
   __shared__ float red[33];
   const int r = blockIdx.x;
   chain_release_if_small();
-  chain_wait(h, delta, rows);
+  chain_wait(h, delta, rows, y, inv, wts);
   const int src = GATHER ? rows[r] : r;
   float* hr = h + (size_t)src * hidden;
   const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
@@ -29,7 +33,13 @@ __global__ void add_layernorm_kernel(float* __restrict__ h, const T* __restrict_
   float s = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = hr[i];
-    if (dr) {
+    if (y) {
+      float acc = 0.f;
+      for (int j = 0; j < k; ++j)
+        acc += (wts ? wts[(size_t)src * k + j] : 1.f) * to_float(y[(size_t)inv[(size_t)src * k + j] * hidden + i]);
+      v += to_float(from_float<T>(acc));
+      if (!GATHER) hr[i] = v;
+    } else if (dr) {
       v += to_float(dr[i]);
       if (!GATHER) hr[i] = v;
     }
@@ -42,9 +52,9 @@ __global__ void add_layernorm_kernel(float* __restrict__ h, const T* __restrict_
     const float d = row[i] - mean;
     ss += d * d;
   }
-  const float inv = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    o[i] = from_float<T>((row[i] - mean) * inv * w[i]);
+    o[i] = from_float<T>((row[i] - mean) * rstd * w[i]);
 }
 
 // out[t, 0:n] = x[t, col0:col0+n] * rsqrt(mean(x^2) + eps) * w   (w may be null: weight 1)
@@ -116,22 +126,36 @@ __global__ void heads_sigmoid_gate_kernel(const T* __restrict__ v, const T* __re
 }
 
 // out[p] = scale[order[p]] * x[order[p] / div]: the tokens in the experts' order, each times the
-// weight of its (token, choice) pair.
-template <typename T>
+// weight of its (token, choice) pair.  VEC: 16 bytes a thread and step (rows are 16-byte aligned).
+template <typename T, bool VEC>
 __global__ void scale_gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ order, int div,
                                          const float* __restrict__ scale, T* __restrict__ out, int hidden,
                                          int n_pairs) {
+  constexpr int VE = 16 / (int)sizeof(T);
   const int p = blockIdx.x;
   chain_wait(x, order, scale);
   const int pair = order[p];
   T* o = out + (size_t)p * hidden;
-  if (pair < 0 || pair >= n_pairs) {
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(0.f);
-    return;
+  const bool bad = pair < 0 || pair >= n_pairs;
+  const float s = bad ? 0.f : scale[pair];
+  const T* xr = x + (size_t)(bad ? 0 : pair / div) * hidden;
+  if (VEC) {
+    for (int i = threadIdx.x * VE; i < hidden; i += blockDim.x * VE) {
+      float v[8];
+      if (sizeof(T) == 2) load8(reinterpret_cast<const __nv_bfloat16*>(xr) + i, v);
+      else load4(reinterpret_cast<const float*>(xr) + i, v);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) v[e] = bad ? 0.f : s * v[e];
+      if (sizeof(T) == 2) {
+        store4(reinterpret_cast<__nv_bfloat16*>(o) + i, v);
+        store4(reinterpret_cast<__nv_bfloat16*>(o) + i + 4, v + 4);
+      } else {
+        store4(reinterpret_cast<float*>(o) + i, v);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(bad ? 0.f : s * to_float(xr[i]));
   }
-  const float s = scale[pair];
-  const T* xr = x + (size_t)(pair / div) * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(s * to_float(xr[i]));
 }
 
 }  // namespace nf
@@ -139,7 +163,8 @@ __global__ void scale_gather_rows_kernel(const T* __restrict__ x, const int* __r
 using namespace nf;
 
 extern "C" int nf_add_layernorm(float* h, const void* delta, const int* rows, const float* w, float eps, void* out,
-                                int R, int hidden, int dtype, cudaStream_t stream) {
+                                int R, int hidden, int dtype, const void* y, const int* inv, const float* wts, int k,
+                                cudaStream_t stream) {
   if (R == 0) return 0;
   NF_REQUIRE(R > 0 && hidden > 0, "add_layernorm: bad sizes R=%d hidden=%d", R, hidden);
   const size_t smem = (size_t)hidden * sizeof(float);
@@ -150,7 +175,7 @@ extern "C" int nf_add_layernorm(float* h, const void* delta, const int* rows, co
     if (smem > 48 * 1024)                                                                                   \
       cudaFuncSetAttribute(add_layernorm_kernel<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     launch_chained(add_layernorm_kernel<T, G>, dim3(R), dim3(threads), smem, stream, h, (const T*)delta, rows, w, \
-                   eps, (T*)out, hidden);                                                                   \
+                   eps, (T*)out, hidden, (const T*)y, inv, wts, k);                                         \
   } while (0)
   if (dtype == kF32) { if (rows) NF_LN(float, true); else NF_LN(float, false); }
   else { if (rows) NF_LN(__nv_bfloat16, true); else NF_LN(__nv_bfloat16, false); }
@@ -208,9 +233,13 @@ extern "C" int nf_scale_gather_rows(const void* x, const int* order, int div, co
                                     int n_rows, int hidden, int dtype, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NF_REQUIRE(div > 0 && hidden > 0, "scale_gather_rows: bad sizes");
-  if (dtype == kF32)
-    launch_chained(scale_gather_rows_kernel<float>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, order, div, scale, (float*)out, hidden, n_rows);
-  else
-    launch_chained(scale_gather_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, (const __nv_bfloat16*)x, order, div, scale, (__nv_bfloat16*)out, hidden, n_rows);
+  const int threads = hidden >= 2048 ? 256 : 128;
+  if (dtype == kF32) {
+    if (hidden % 4 == 0) launch_chained(scale_gather_rows_kernel<float, true>, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, order, div, scale, (float*)out, hidden, n_rows);
+    else launch_chained(scale_gather_rows_kernel<float, false>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, order, div, scale, (float*)out, hidden, n_rows);
+  } else {
+    if (hidden % 8 == 0) launch_chained(scale_gather_rows_kernel<__nv_bfloat16, true>, dim3(n_rows), dim3(threads), 0, stream, (const __nv_bfloat16*)x, order, div, scale, (__nv_bfloat16*)out, hidden, n_rows);
+    else launch_chained(scale_gather_rows_kernel<__nv_bfloat16, false>, dim3(n_rows), dim3(256), 0, stream, (const __nv_bfloat16*)x, order, div, scale, (__nv_bfloat16*)out, hidden, n_rows);
+  }
   return check_launch("scale_gather_rows");
 }

@@ -950,17 +950,26 @@ def moe_combine_add_rmsnorm(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, s
 # ---------------------------------------------------------------------------------------
 
 def add_layernorm(h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor],
-                  weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+                  weight: torch.Tensor, eps: float, out: torch.Tensor, routed=None) -> None:
     """h += delta (float32, in place); out = (h - mean) * rsqrt(var + eps) * weight, var the mean of
-    the squared deviations.  With `rows`: out[r] from h[rows[r]] + delta[rows[r]], h left alone."""
+    the squared deviations.  With `rows`: out[r] from h[rows[r]] + delta[rows[r]], h left alone.
+    `routed` = (y, inv, wts or None, k) instead of `delta`: the routed experts' pending sum
+    sum_j wts[t, j] * y[inv[t * k + j]] is added up inside the kernel (same bits as `moe_combine` first)."""
     _chk(h, "h", torch.float32); _chk(weight, "weight", torch.float32); _chk(out, "out")
     if delta is not None:
         _chk(delta, "delta", out.dtype)
     if rows is not None:
         _chk(rows, "rows", torch.int32)
+    y = inv = wts = None
+    k = 0
+    if routed is not None:
+        y, inv, wts, k = routed
+        _chk(y, "y", out.dtype); _chk(inv, "inv", torch.int32)
+        if wts is not None:
+            _chk(wts, "wts", torch.float32)
     R = h.shape[0] if rows is None else rows.numel()
     _lib.call("nf_add_layernorm", _p(h), _p(delta), _p(rows), _p(weight), c_float(eps), _p(out), c_int(R),
-              c_int(h.shape[1]), c_int(_dt(out)), _stream())
+              c_int(h.shape[1]), c_int(_dt(out)), _p(y), _p(inv), _p(wts), c_int(k), _stream())
 
 
 def rms_norm_slice(x: torch.Tensor, col0: int, n: int, weight: Optional[torch.Tensor], eps: float) -> torch.Tensor:
@@ -1035,12 +1044,14 @@ SCAN_MAX_STATE = 256
 def causal_conv_silu(src: torch.Tensor, col0: int, C: int, taps: torch.Tensor, bias: Optional[torch.Tensor],
                      state: torch.Tensor, ctx) -> torch.Tensor:
     """silu(bias + causal convolution per channel) of columns [col0, col0 + C) of src [T, ld] -> [T, C].
-    taps float32 [C, K] (last column: the current token).  `state` float32 [slots, >= (K - 1) * C]:
+    taps float32 [K, C], tap-major (last row: the current token's).  `state` float32 [slots, >= (K - 1) * C]:
     each request's last K - 1 inputs, read for the positions before this step and replaced by
     the step's last inputs afterwards."""
     _chk(src, "src"); _chk(taps, "taps", torch.float32); _chk(state, "state", torch.float32)
     T, ld = src.shape
-    K = taps.shape[1]
+    K = taps.shape[0]
+    if taps.shape[1] != C:
+        raise ValueError("causal_conv_silu: taps must be [K, C]")
     out = torch.empty((T, C), dtype=src.dtype, device=src.device)
     _lib.call("nf_causal_conv_silu", _p(src), c_int(ld), c_int(col0), c_int(C), _p(taps), _p(bias), c_int(K),
               _p(state), c_longlong(state.stride(0)), _p(ctx.row_seg), _p(ctx.seg_row0), _p(ctx.seg_slot), _p(out),

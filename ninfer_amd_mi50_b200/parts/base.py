@@ -279,14 +279,17 @@ class RoutedSum:
     """
     y: torch.Tensor                      # [T * k, hidden] expert outputs in sorted order
     plan: object                         # the routing plan (`inv` is what is used)
-    wts: torch.Tensor                    # float32 [T, k]
+    wts: Optional[torch.Tensor]          # float32 [T, k]; None: every weight is 1
     shared: Optional[torch.Tensor]       # [T, hidden] or None
     gate: Optional[torch.Tensor]         # float32 [T, 1] gate logits or None
     dtype: torch.dtype = torch.bfloat16
 
     def materialize(self) -> torch.Tensor:
         from .. import kernels
-        return kernels.moe_combine(self.y, self.plan, self.wts, self.shared, self.gate, self.dtype)
+        wts = self.wts
+        if wts is None:
+            wts = torch.ones((self.plan.num_tokens, self.plan.top_k), dtype=torch.float32, device=self.y.device)
+        return kernels.moe_combine(self.y, self.plan, wts, self.shared, self.gate, self.dtype)
 
 
 def summed(delta):

@@ -282,7 +282,7 @@ class SparseMoeSwiglu(FeedForward):
             SparseMoeSwiglu.record_routing.append(idx.clone())
         if self.weight_on == "input":
             y = kernels.moe_experts_sorted(kernels.scale_gather_rows(x, plan, k, wts), self.w13, self.w2, plan)
-            wts = torch.ones_like(wts)
+            wts = None                          # the weights are spent: the sum adds the outputs as they are
         else:
             y = kernels.moe_experts(x, self.w13, self.w2, plan, k)
         shared = None

@@ -37,7 +37,7 @@ class RmsNorm(Norm):
         return self.size * 4
 
     def _fusable(self, delta, out_dtype, rows: int) -> bool:
-        return (isinstance(delta, RoutedSum) and out_dtype == torch.bfloat16
+        return (isinstance(delta, RoutedSum) and out_dtype == torch.bfloat16 and delta.wts is not None
                 and kernels.can_fuse_combine_norm(delta.y, self.size, rows, delta.wts.shape[1]))
 
     def add_norm(self, h, delta, out_dtype):
@@ -67,6 +67,7 @@ class LayerNorm(Norm):
     deviations from the mean.  Sum, mean, variance and product are 32-bit in both modes."""
 
     graph_safe = True
+    takes_unsummed = True
 
     def __init__(self, size: int, eps: float, prefix: str, weight_name: str = "weight"):
         self.size, self.eps, self.prefix, self.weight_name = int(size), float(eps), prefix, weight_name
@@ -85,12 +86,22 @@ class LayerNorm(Norm):
     def weight_bytes(self) -> int:
         return self.size * 4
 
+    @staticmethod
+    def _routed(delta, out_dtype):
+        """The routed experts' pending sum in the form the kernel adds up itself, or None."""
+        if (isinstance(delta, RoutedSum) and delta.shared is None and delta.y.dtype == out_dtype
+                and delta.plan.top_k <= kernels.FUSED_COMBINE_MAX_K):
+            return (delta.y, delta.plan.inv, delta.wts, delta.plan.top_k)
+        return None
+
     def add_norm(self, h, delta, out_dtype):
         out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
-        kernels.add_layernorm(h, summed(delta), None, self.weight, self.eps, out)
+        routed = self._routed(delta, out_dtype)
+        kernels.add_layernorm(h, None if routed else summed(delta), None, self.weight, self.eps, out, routed=routed)
         return out
 
     def add_norm_rows(self, h, delta, rows, out_dtype):
         out = torch.empty((rows.numel(), h.shape[1]), dtype=out_dtype, device=h.device)
-        kernels.add_layernorm(h, summed(delta), rows, self.weight, self.eps, out)
+        routed = self._routed(delta, out_dtype)
+        kernels.add_layernorm(h, None if routed else summed(delta), rows, self.weight, self.eps, out, routed=routed)
         return out

@@ -74,7 +74,8 @@ class StateSpaceDual(Mixer):
 
     def load(self, fetch: Fetch) -> None:
         self.w_in, self.w_out = fetch(self._n("in")), fetch(self._n("out"))
-        self.conv_w, self.conv_b = fetch(self._n("conv")).contiguous(), fetch(self._n("conv_bias"))
+        # the checkpoint's taps are [channels, taps]; the kernel reads them tap-major
+        self.conv_w, self.conv_b = fetch(self._n("conv")).t().contiguous(), fetch(self._n("conv_bias"))
         self.dt_bias, self.A_log, self.D = fetch(self._n("dt_bias")), fetch(self._n("A_log")), fetch(self._n("D"))
         self.norm_w = fetch(self._n("norm"))
 
