@@ -95,18 +95,19 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, const __nv_
   const int b_end = min(b_begin + blocks_per_split, last_pos / kLmKeys + 1);      // last_pos >= 0 for a real tile
   const int* bt = block_table + (size_t)seg * bt_width;
 
+  // Four threads a key row: the row's page is looked up once, then 16-byte copies at a stride of four.
   auto fetch = [&](int blk, int buf) {
-    __nv_bfloat16* dst = Ks + (size_t)buf * kLmKeys * WS;
-    for (int i = threadIdx.x; i < kLmKeys * chunks; i += kLmThreads) {
-      const int r = i / chunks, c = (i - r * chunks) * 8;
-      const int j = blk * kLmKeys + r;
-      const int lp = j / page_size;
-      const int page = (j <= last_pos && lp < bt_width) ? bt[lp] : -1;
-      __nv_bfloat16* d = dst + r * WS + c;
-      if (page >= 0 && page < num_pages)
-        lm_cp16(lm_smem(d), pages + ((size_t)page * page_size + (j % page_size)) * W + c);
-      else
-        *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);     // a masked key's row must still be finite
+    const int r = threadIdx.x >> 2;                                  // 256 threads, 64 rows
+    const int j = blk * kLmKeys + r;
+    const int lp = j / page_size;
+    const int page = (j <= last_pos && lp < bt_width) ? bt[lp] : -1;
+    __nv_bfloat16* d = Ks + ((size_t)buf * kLmKeys + r) * WS;
+    if (page >= 0 && page < num_pages) {
+      const __nv_bfloat16* src = pages + ((size_t)page * page_size + (j - lp * page_size)) * W;
+      for (int c = (threadIdx.x & 3) * 8; c < W; c += 32) lm_cp16(lm_smem(d + c), src + c);
+    } else {
+      for (int c = (threadIdx.x & 3) * 8; c < W; c += 32)
+        *reinterpret_cast<uint4*>(d + c) = make_uint4(0, 0, 0, 0);   // a masked key's row must still be finite
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
