@@ -137,28 +137,39 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, const __nv_
     if (blk + 1 < b_end) fetch(blk + 1, buf ^ 1);      // into the buffer that block used; lands during this one's work
     const __nv_bfloat16* Kb = Ks + (size_t)buf * kLmKeys * WS;
     // ---- S = Q K^T for this warp's 8 keys ----
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // (two sums a 16-row half, over the even and the odd steps of 16 columns: a sum's products wait for
+    // one another, and with one sum a half the tensor pipe idled between them)
+    float s[2][4], s_odd[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[mt][e] = s_odd[mt][e] = 0.f;
     {
       const unsigned qa = lm_smem(Qs + (lane & 15) * WS + (lane >> 4) * 8);
       const unsigned ka = lm_smem(Kb + (warp * 8 + (lane & 7)) * WS + (lane >> 3) * 8);
       for (int k0 = 0; k0 < W; k0 += 32) {
         unsigned b0, b1, b2, b3;
-        if (k0 + 16 < W) lm_ldm4(ka + k0 * 2, b0, b1, b2, b3);
-        else {                                          // W is a multiple of 16, not always of 32
+        const bool both = k0 + 16 < W;                  // W is a multiple of 16, not always of 32
+        if (both) lm_ldm4(ka + k0 * 2, b0, b1, b2, b3);
+        else {
           asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(ka + k0 * 2));
           b2 = b3 = 0;
         }
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-          if (k0 + kk * 16 >= W) break;
-#pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
-            unsigned a0, a1, a2, a3;
-            lm_ldm4(qa + (mt * 16 * WS + k0 + kk * 16) * 2, a0, a1, a2, a3);
-            lm_mma(s[mt], a0, a1, a2, a3, kk ? b2 : b0, kk ? b3 : b1);
+        for (int mt = 0; mt < 2; ++mt) {
+          unsigned a0, a1, a2, a3;
+          lm_ldm4(qa + (mt * 16 * WS + k0) * 2, a0, a1, a2, a3);
+          lm_mma(s[mt], a0, a1, a2, a3, b0, b1);
+          if (both) {
+            lm_ldm4(qa + (mt * 16 * WS + k0 + 16) * 2, a0, a1, a2, a3);
+            lm_mma(s_odd[mt], a0, a1, a2, a3, b2, b3);
           }
         }
       }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[mt][e] += s_odd[mt][e];
     }
     // ---- mask, block maxima ----
     const int key0 = blk * kLmKeys + warp * 8 + (lane & 3) * 2;
