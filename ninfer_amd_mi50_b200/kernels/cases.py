@@ -138,7 +138,60 @@ def case_small_decode(batch: int, device):
             ("combine_add_rmsnorm", lambda: moe_combine_add_rmsnorm(y, plan, wts, delta, gate, h, None, w, 1e-6, out))]
 
 
+def _one_request(tokens: int, device, single: bool = False, context: int = 0):
+    """Step metadata for one prompt of `tokens` rows, or (`single`) `tokens` requests of one row at `context`."""
+    from ..parts.base import StepContext
+    if single:
+        pos = torch.full((tokens,), context, dtype=torch.int32)
+        seg, row0, lens, pos0, S = torch.arange(tokens, dtype=torch.int32), torch.arange(tokens + 1, dtype=torch.int32), [1] * tokens, [context] * tokens, tokens
+    else:
+        pos = torch.arange(tokens, dtype=torch.int32)
+        seg, row0, lens, pos0, S = torch.zeros(tokens, dtype=torch.int32), torch.tensor([0, tokens], dtype=torch.int32), [tokens], [0], 1
+    z = torch.zeros(1, dtype=torch.int32, device=device)
+    return StepContext(dtype=torch.bfloat16, device=torch.device(device), T=tokens, S=S, token_ids=z, positions=pos.to(device),
+                       row_seg=seg.to(device), seg_row0=row0.to(device), seg_pos0=z, seg_slot=torch.arange(S, dtype=torch.int32, device=device),
+                       logit_rows=z, seg_len_host=lens, seg_pos0_host=pos0, max_rows_per_seg=max(lens),
+                       max_context=(context + 1) if single else tokens)
+
+
+def case_latent_attention(tokens: int, device, single: bool = False, context: int = 0):
+    """Attention over latent rows (width 512 + 64 rotated, HQ heads): a prompt of `tokens` rows, or
+    `tokens` decoded rows that each see `context` cached rows."""
+    from . import latent_attention
+    R, Dr, dim = 512, 64, 128
+    ctx = _one_request(tokens, device, single, context)
+    held = (context + 1) if single else tokens
+    per = (held + PAGE - 1) // PAGE
+    pages = (torch.randn(ctx.S * per + 1, PAGE, R + Dr, device=device) * 0.5).bfloat16()
+    bt = torch.arange(ctx.S * per, dtype=torch.int32, device=device).view(ctx.S, per)
+    q_abs = (torch.randn(HQ, tokens, R, device=device) * 0.1).bfloat16()
+    q = (torch.randn(tokens, HQ * (dim + Dr), device=device) * 0.1).bfloat16()
+    sink = torch.zeros(HQ, device=device)
+    return [("latent_attention", lambda: latent_attention(q_abs, q, dim + Dr, dim, Dr, pages, bt, PAGE, ctx, sink, 0.07))]
+
+
+def case_state_space(tokens: int, device, single: bool = False):
+    """The convolution and the selective scan of a state-space mixer with 2 H inner channels (heads of 64,
+    state 128, 8 groups): a prompt of `tokens` rows, or `tokens` requests of one row."""
+    from . import causal_conv_silu, ssd_scan
+    heads, P, N, G, K = 2 * H // 64, 64, 128, 8, 4
+    inner = heads * P
+    C = inner + 2 * G * N
+    ctx = _one_request(tokens, device, single)
+    proj = (torch.randn(tokens, 2 * inner + 2 * G * N + heads, device=device) * 0.5).bfloat16()
+    state = torch.zeros(ctx.S + 1, (K - 1) * C + heads * P * N, device=device)
+    taps, bias, z = torch.randn(K, C, device=device) * 0.3, torch.zeros(C, device=device), torch.zeros(heads, device=device)
+    xbc = causal_conv_silu(proj, inner, C, taps, bias, state, ctx)
+    return [("causal_conv_silu", lambda: causal_conv_silu(proj, inner, C, taps, bias, state, ctx)),
+            ("ssd_scan", lambda: ssd_scan(xbc, 0, inner, inner + G * N, proj, 2 * inner + 2 * G * N, z, z, z, state,
+                                          (K - 1) * C, ctx, heads, P, N, G))]
+
+
 CASES = {
+    "latent_attention_prefill": lambda dev: case_latent_attention(2048, dev),
+    "latent_attention_decode8": lambda dev: case_latent_attention(8, dev, True, 2048),
+    "state_space_prefill": lambda dev: case_state_space(2048, dev),
+    "state_space_decode8": lambda dev: case_state_space(8, dev, True),
     "moe_prefill": lambda dev: case_moe(2048, dev),
     "moe_decode8": lambda dev: case_moe(8, dev),
     "moe_decode64": lambda dev: case_moe(64, dev),
