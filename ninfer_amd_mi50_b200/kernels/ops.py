@@ -1086,6 +1086,7 @@ def ssd_scan(xbc: torch.Tensor, x_col0: int, b_col0: int, c_col0: int, dt_src: t
 LATENT_MAX_RANK = 512
 LATENT_TILE_PAIRS = 32      # (token, head) pairs a tile of the tensor-core kernel
 LATENT_KEY_BLOCK = 64       # keys a block of that kernel
+LATENT_SPLIT_CTAS = 148     # long contexts are split until about this many CTAs run (one a SM)
 
 
 def latent_append(src: torch.Tensor, col0: int, R: int, Dr: int, weight: torch.Tensor, eps: float,
@@ -1134,7 +1135,7 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, head_stride: int, rot
         else:
             tiles, n_tiles = ctx.pair_tiles(heads, LATENT_TILE_PAIRS)
         n_blocks = max(1, (int(ctx.max_context) + LATENT_KEY_BLOCK - 1) // LATENT_KEY_BLOCK)
-        nsplit = min(n_blocks, max(1, (2 * 148 + n_tiles - 1) // n_tiles))
+        nsplit = min(n_blocks, max(1, (LATENT_SPLIT_CTAS + n_tiles - 1) // n_tiles))
         per_split = (n_blocks + nsplit - 1) // nsplit
         nsplit = (n_blocks + per_split - 1) // per_split
         ws_o = torch.empty((T * heads, nsplit, R), dtype=torch.float32, device=q_abs.device)
