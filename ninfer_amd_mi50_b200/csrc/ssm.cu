@@ -182,8 +182,8 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ldx, int x_col0, int b_col0, int 
           if (sizeof(T) == 2) {
             float f[8];
             unpack8(pre[k], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dst[e] = f[e];
+            store4(dst, f);                      // (16 bytes a store: eight scalar stores met eight-way bank conflicts)
+            store4(dst + 4, f + 4);
           } else {
             *reinterpret_cast<uint4*>(dst) = pre[k];
           }
