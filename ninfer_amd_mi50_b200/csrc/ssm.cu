@@ -10,7 +10,7 @@
 //    y_t = S_t^T C_t + D x_t  with dt_t = softplus(raw_t + dt_bias), per head; S is [N, P]
 //    float32 per head and lives in the slot.  One CTA owns a slice of a head's P columns for one
 //    request and walks that request's rows of the step in order; a column's N states are spread
-//    over 16 lanes (registers), so y's sum over N is a 16-lane shuffle in a fixed order.  The
+//    over a warp's lanes (registers), so y's sum over N is a shuffle reduction in a fixed order.  The
 //    step's B, C, x and dt are staged through shared memory sixteen tokens at a time.  A token's
 //    result depends on the tokens before it only through S, which is the same bits however the
 //    request was cut into steps.
@@ -95,14 +95,14 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ src, int lds, int 
   for (int i = 0; i < K - 1; ++i) st[(size_t)i * C + c] = keep[i];
 }
 
-constexpr int kScanLanes = 16;     // lanes that share one column's N states
-constexpr int kScanGroups = 8;     // groups of such lanes a CTA
+constexpr int kScanLanes = 32;     // lanes that share one column's N states: a warp
+constexpr int kScanGroups = 8;     // warps a CTA
 constexpr int kScanThreads = kScanLanes * kScanGroups;
 constexpr int kScanChunk = 16;     // tokens staged at a time
-constexpr int kScanMaxPer = 16;    // N <= 256
-constexpr int kScanStage = 8;      // 16-byte loads a thread keeps in flight for the next chunk
+constexpr int kScanMaxPer = 8;     // N <= 256
+constexpr int kScanStage = 4;      // 16-byte loads a thread keeps in flight for the next chunk
 
-// CP: columns of P a thread owns (its group of 16 lanes owns CP columns, the CTA 8 * CP): a token's
+// CP: columns of P a thread owns (its warp owns CP columns, the CTA 8 * CP): a token's
 // B and C are read from shared memory once for all of them.
 template <typename T, int NPER, int CP>
 __global__ void __launch_bounds__(kScanThreads)
@@ -145,10 +145,11 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ldx, int x_col0, int b_col0, int 
   const int vpr = N / VE;                                         // 16-byte pieces of one token's B (or C)
   const bool vec = (N % VE == 0) && (ldx % VE == 0) && ((b_col0 + g * N) % VE == 0) && ((c_col0 + g * N) % VE == 0) &&
                    (2 * kScanChunk * vpr <= kScanStage * kScanThreads);
+  constexpr int XI = (kScanChunk * kCols + kScanThreads - 1) / kScanThreads;     // x values a thread stages
   uint4 pre[kScanStage];
-  float pre_x[CP], pre_dt = 0.f;
+  float pre_x[XI], pre_dt = 0.f;
 #pragma unroll
-  for (int c = 0; c < CP; ++c) pre_x[c] = 0.f;
+  for (int c = 0; c < XI; ++c) pre_x[c] = 0.f;
   auto issue = [&](int c0) {
     const int nc = min(kScanChunk, n_rows - c0);
 #pragma unroll
@@ -161,8 +162,8 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ldx, int x_col0, int b_col0, int 
       }
     }
 #pragma unroll
-    for (int c = 0; c < CP; ++c) {
-      const int idx = threadIdx.x + c * kScanThreads;              // chunk * cols = threads * CP
+    for (int c = 0; c < XI; ++c) {
+      const int idx = threadIdx.x + c * kScanThreads;
       const int tt = idx / kCols, pp = idx - tt * kCols;
       pre_x[c] = (tt < nc && p0 + pp < P) ? to_float(xbc[(size_t)(r0 + c0 + tt) * ldx + x_col0 + h * P + p0 + pp]) : 0.f;
     }
@@ -190,7 +191,8 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ldx, int x_col0, int b_col0, int 
         }
       }
 #pragma unroll
-      for (int c = 0; c < CP; ++c) xs[threadIdx.x + c * kScanThreads] = pre_x[c];
+      for (int c = 0; c < XI; ++c)
+        if (threadIdx.x + c * kScanThreads < kScanChunk * kCols) xs[threadIdx.x + c * kScanThreads] = pre_x[c];
       if (threadIdx.x < nc) {
         const float v = pre_dt + bias;
         const float dt = v > 20.f ? v : log1pf(expf(v));
@@ -300,10 +302,11 @@ static void launch_scan_cp(const void* xbc, int ldx, int x_col0, int b_col0, int
   if (nper <= 1) NF_SCAN(1);
   else if (nper <= 2) NF_SCAN(2);
   else if (nper <= 4) NF_SCAN(4);
-  else if (nper <= 8) NF_SCAN(8);
-  else if (CP <= 2) NF_SCAN(16);           // (N > 128 with four columns a thread would not fit the registers)
+  else NF_SCAN(8);
 #undef NF_SCAN
 }
+
+static int g_scan_columns = 0;      // nf_set_scan_columns(): 1, 2 or 4 forces the choice below (measurement)
 
 // Columns a thread: as many as keep at least one CTA a SM busy and the states in registers.
 template <typename T>
@@ -312,9 +315,10 @@ static int launch_scan(const void* xbc, int ldx, int x_col0, int b_col0, int c_c
                        long slot_stride, const int* seg_row0, const int* seg_slot, float* y, int S, int heads, int P,
                        int N, int groups, cudaStream_t stream) {
   const long ctas4 = (long)S * heads * ((P + 31) / 32), ctas2 = (long)S * heads * ((P + 15) / 16);
-  if (N <= 128 && P % 32 == 0 && ctas4 >= 148)
+  const int forced = g_scan_columns;
+  if (forced == 4 ? P % 32 == 0 : (forced == 0 && P % 32 == 0 && ctas4 >= 148))
     launch_scan_cp<T, 4>(xbc, ldx, x_col0, b_col0, c_col0, dt_src, ld_dt, dt_col0, dt_bias, A_log, Dskip, state, slot_stride, seg_row0, seg_slot, y, S, heads, P, N, groups, stream);
-  else if (P % 16 == 0 && ctas2 >= 148)
+  else if (forced == 2 ? P % 16 == 0 : (forced == 0 && P % 16 == 0 && ctas2 >= 148))
     launch_scan_cp<T, 2>(xbc, ldx, x_col0, b_col0, c_col0, dt_src, ld_dt, dt_col0, dt_bias, A_log, Dskip, state, slot_stride, seg_row0, seg_slot, y, S, heads, P, N, groups, stream);
   else
     launch_scan_cp<T, 1>(xbc, ldx, x_col0, b_col0, c_col0, dt_src, ld_dt, dt_col0, dt_bias, A_log, Dskip, state, slot_stride, seg_row0, seg_slot, y, S, heads, P, N, groups, stream);
@@ -324,6 +328,8 @@ static int launch_scan(const void* xbc, int ldx, int x_col0, int b_col0, int c_c
 }  // namespace nf
 
 using namespace nf;
+
+extern "C" void nf_set_scan_columns(int columns) { g_scan_columns = columns; }
 
 extern "C" int nf_causal_conv_silu(const void* src, int lds, int col0, int C, const float* taps, const float* bias,
                                    int K, float* state, long long slot_stride, const int* row_seg,
