@@ -32,7 +32,7 @@ def parse_ids(text: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="ninfer", description="Qwen2-MoE generation on one B200")
+    ap = argparse.ArgumentParser(prog="ninfer", description="generation on one B200 from a model folder (Qwen2-MoE, Vekasun)")
     ap.add_argument("model_dir")
     ap.add_argument("--prompt", help="one-shot generation from text (needs tokenizer.json)")
     ap.add_argument("--system", default="", help="system message")

@@ -390,3 +390,31 @@ def test_trace_replay_program_runs_the_design(folder, tmp_path):
             assert torch.equal(arr[at:at + n], got[e["id"]][rows[e["id"]]:rows[e["id"]] + n])
             at += n
             rows[e["id"]] += n
+
+
+@pytest.mark.parametrize("how", ["folder", "seed"])
+def test_the_command_line_generates_from_the_design(tmp_path, how):
+    """`bin/ninfer` on a Vekasun folder, and on a folder with only config.json and a seed."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg0, seed = VC.CONFIGS["straight"]
+    d = str(tmp_path / "m")
+    VC.write_folder(cfg0, seed, d)
+    cfg, w = VC.read_folder(d)
+    if how == "seed":
+        os.remove(os.path.join(d, "model.safetensors"))
+    prompt = random_tokens(30, cfg["vocab"], 12)
+    cmd = [sys.executable, os.path.join(root, "bin", "ninfer"), d, "--prompt-ids", ",".join(map(str, prompt)),
+           "--temperature", "0", "--max-new", "6", "--dtype", "fp32", "--prefill-chunk", "16", "--repeat-penalty", "1"]
+    if how == "seed":
+        cmd += ["--random-weights", str(seed)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    got = [int(x) for x in p.stdout.split()]
+    assert len(got) == 6
+    seq = list(prompt)
+    for t in got:
+        lg = PV.forward(cfg, w, seq)[-1]
+        assert float(lg[t]) >= float(lg.max()) - 1e-4 * float(lg.abs().max())
+        seq.append(t)
