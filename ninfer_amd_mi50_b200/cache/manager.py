@@ -194,6 +194,11 @@ class CacheManager:
                     self.pages_cleared += 1
         ent.reserved = max(ent.reserved, new_length)
 
+    def _first_droppable_page(self, g: CacheGroup) -> int:
+        """First logical page that holds none of the entries a window group keeps for good."""
+        keep = int(getattr(g.spec, "keep_first", 0) or 0)
+        return (keep + self.page_size - 1) // self.page_size
+
     def commit(self, req: Hashable, new_length: int) -> None:
         """The step wrote positions < new_length; release what a window has passed."""
         ent = self.requests[req]
@@ -202,7 +207,7 @@ class CacheManager:
         ent.length = new_length
         for g, table in zip(self.groups, ent.tables):
             first = self._first_live_page(g, new_length)
-            dead = [i for i in range(min(first, len(table))) if table[i] >= 0]
+            dead = [i for i in range(self._first_droppable_page(g), min(first, len(table))) if table[i] >= 0]
             if dead:
                 g.pool.give_back([table[i] for i in dead])
                 for i in dead:

@@ -96,6 +96,8 @@ class ModelPlan:
     logit_scale: float = 1.0                                    # logits = head x * logit_scale
     # float32 tables [rows, hidden] whose rows the order may add to the stream: (name, rows)
     stream_vectors: Tuple[Tuple[str, int], ...] = ()
+    # parts of the "embedding" registry whose rows are added to the token embedding
+    embedding_extras: Tuple[PartSpec, ...] = ()
 
 
 # --------------------------------------------------------------------------------------

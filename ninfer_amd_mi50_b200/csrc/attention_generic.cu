@@ -8,6 +8,11 @@
 // Scores, max, exp, sums and the accumulator are float32.  Keys are visited in blocks of
 // 32 in ascending order from `lo`, so a row's result depends only on its own position,
 // never on how the prompt was cut or what else is in the batch.
+//
+// Options beside the reference's mathematics: `slopes` (one per query head) takes
+// slope_h * (p - j) off the score of key j; `keep_first` keeps the first keys of a request
+// visible when the window has passed them (at their true positions); `gate` multiplies head h's
+// output by sigmoid(gate[t, h]).
 #include "common.cuh"
 
 namespace nf {
@@ -21,7 +26,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_row_stride,
                                int bt_width, const int* __restrict__ positions,
                                const int* __restrict__ row_seg, T* __restrict__ out, int Hq,
                                int Hkv, int D, int page_size, int num_pages, int window,
-                               float scale) {
+                               float scale, const float* __restrict__ slopes, int keep_first,
+                               const float* __restrict__ gate, int gate_ld) {
   extern __shared__ float q_smem[];          // [4 warps][D]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -45,12 +51,17 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_row_stride,
   float acc[kMaxDimsPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxDimsPerLane; ++i) acc[i] = 0.f;
+  const float slope = slopes ? slopes[h] : 0.f;
+  // two runs of keys: the kept first ones that lie before the window, then the window
+  const int kept_end = min(keep_first, lo);
 
-  for (int j0 = lo; j0 <= pos; j0 += 32) {
+  for (int run = 0; run < 2; ++run) {
+  const int first = run == 0 ? 0 : lo, last = run == 0 ? kept_end - 1 : pos;
+  for (int j0 = first; j0 <= last; j0 += 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
     const T* vrow = nullptr;
-    if (j <= pos) {
+    if (j <= last) {
       const int lp = j / page_size;
       const int page = lp < bt_width ? bt[lp] : -1;
       if (page >= 0 && page < num_pages) {
@@ -64,7 +75,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_row_stride,
 #pragma unroll
           for (int e = 0; e < 8; ++e) dot = fmaf(q[d + e], kk[e], dot);
         }
-        s = dot * scale;
+        s = dot * scale - slope * (float)(pos - j);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -75,7 +86,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_row_stride,
     m = m_new;
 #pragma unroll
     for (int i = 0; i < kMaxDimsPerLane; ++i) acc[i] *= alpha;
-    const int nkeys = min(32, pos - j0 + 1);
+    const int nkeys = min(32, last - j0 + 1);
     for (int jj = 0; jj < nkeys; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const unsigned long long vp = __shfl_sync(0xffffffffu, (unsigned long long)vrow, jj);
@@ -88,7 +99,9 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_row_stride,
       }
     }
   }
-  const float inv_l = l > 0.f ? 1.f / l : 0.f;
+  }
+  float inv_l = l > 0.f ? 1.f / l : 0.f;
+  if (gate) inv_l *= 1.f / (1.f + expf(-gate[(size_t)t * gate_ld + h]));
   T* o = out + (size_t)t * Hq * D + (size_t)h * D;
 #pragma unroll
   for (int i = 0; i < kMaxDimsPerLane; ++i) {
@@ -106,6 +119,7 @@ extern "C" int nf_paged_attention_generic(const void* qkv, int q_row_stride, con
                                           const int* positions, const int* row_seg, void* out,
                                           int T, int Hq, int Hkv, int D, int page_size,
                                           int num_pages, int window, float scale, int dtype,
+                                          const float* slopes, int keep_first, const float* gate, int gate_ld,
                                           cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: bad sizes T=%d Hq=%d Hkv=%d", T, Hq, Hkv);
@@ -113,8 +127,8 @@ extern "C" int nf_paged_attention_generic(const void* qkv, int q_row_stride, con
   dim3 grid(T, (Hq + 3) / 4);
   const size_t smem = 4 * D * sizeof(float);
   if (dtype == kF32)
-    paged_attention_generic_kernel<float><<<grid, 128, smem, stream>>>((const float*)qkv, q_row_stride, (const float*)pages, block_table, bt_width, positions, row_seg, (float*)out, Hq, Hkv, D, page_size, num_pages, window, scale);
+    paged_attention_generic_kernel<float><<<grid, 128, smem, stream>>>((const float*)qkv, q_row_stride, (const float*)pages, block_table, bt_width, positions, row_seg, (float*)out, Hq, Hkv, D, page_size, num_pages, window, scale, slopes, keep_first, gate, gate_ld);
   else
-    paged_attention_generic_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions, row_seg, (__nv_bfloat16*)out, Hq, Hkv, D, page_size, num_pages, window, scale);
+    paged_attention_generic_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions, row_seg, (__nv_bfloat16*)out, Hq, Hkv, D, page_size, num_pages, window, scale, slopes, keep_first, gate, gate_ld);
   return check_launch("paged_attention_generic");
 }

@@ -213,4 +213,24 @@ __device__ __forceinline__ void load8(const float* p, float* out) {
   out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
 }
 
+// The gated activation of a feed-forward's first product, from the gate's and the up projection's
+// float32 sums.  kind 1: silu(g) * u.  kind 2 (capped): g' = min(g, limit), u' = clamp(u, -limit,
+// limit); g' * sigmoid(alpha * g') * (u' + 1).
+enum GatedAct : int { kActNone = 0, kActSilu = 1, kActCapped = 2 };
+struct GatedActParams {
+  int kind;       // GatedAct
+  float limit, alpha;
+};
+__device__ __forceinline__ float gated_act(float g, float u, int kind, float limit, float alpha) {
+  if (kind == kActCapped) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
+__device__ __forceinline__ float gated_act(float g, float u, const GatedActParams& a) {
+  return gated_act(g, u, a.kind, a.limit, a.alpha);
+}
+
 }  // namespace nf

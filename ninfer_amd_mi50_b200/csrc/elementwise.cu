@@ -418,3 +418,108 @@ extern "C" int nf_gather_rows(const void* x, const int* rows, int div, void* out
   launch_chained(gather_rows_kernel, dim3(n), dim3(row_threads(row_bytes / 16)), 0, stream, (const uint4*)x, rows, div, (uint4*)out, row_bytes / 16);
   return check_launch("gather_rows");
 }
+
+// ---------------------------------------------------------------------------------------------
+// A second embedding looked up by a hash of (previous token, token), added to the stream, and
+// the gated activation with biases.
+// ---------------------------------------------------------------------------------------------
+namespace nf {
+
+// h[t] += table[row(t)], row(t) = (prev * mul_prev + id * mul_cur) mod buckets, or `buckets` (the
+// table's last row) for a request's first token.  The previous token of a segment's first row is
+// what the request's slot remembers (`last[slot]` = token + 1; 0: none yet); the CTA of that row
+// also leaves the segment's last token there for the next step.
+template <typename T>
+__global__ void pair_hash_embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                       const int* __restrict__ row_seg, const int* __restrict__ seg_row0,
+                                       const int* __restrict__ seg_slot, int* __restrict__ last, long slot_stride,
+                                       float* __restrict__ h, int hidden, int buckets, unsigned long long mul_prev,
+                                       unsigned long long mul_cur) {
+  __shared__ int s_prev;
+  const int t = blockIdx.x;
+  chain_wait(h, last);
+  const int seg = row_seg[t], r0 = seg_row0[seg];
+  if (threadIdx.x == 0) {
+    if (t == r0) {
+      int* slot = last + (size_t)seg_slot[seg] * slot_stride;
+      s_prev = *slot - 1;
+      *slot = ids[seg_row0[seg + 1] - 1] + 1;
+    } else {
+      s_prev = ids[t - 1];
+    }
+  }
+  __syncthreads();
+  const int prev = s_prev;
+  const unsigned long long row =
+      prev < 0 ? (unsigned long long)buckets
+               : ((unsigned long long)prev * mul_prev + (unsigned long long)ids[t] * mul_cur) % (unsigned long long)buckets;
+  const T* tr = table + (size_t)row * hidden;
+  float* hr = h + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) hr[i] += to_float(tr[i]);
+}
+
+// act[m, i] = gated_act(gu[m, i] + bias[i], gu[m, inner + i] + bias[inner + i]); gu is float32 or T.
+template <typename TI, typename T>
+__global__ void gated_bias_act_kernel(const TI* __restrict__ gu, const float* __restrict__ bias, T* __restrict__ act,
+                                      int inner, int kind, float limit, float alpha) {
+  const int m = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  chain_wait(gu);
+  if (i >= inner) return;
+  float g = to_float(gu[(size_t)m * 2 * inner + i]), u = to_float(gu[(size_t)m * 2 * inner + inner + i]);
+  if (bias) { g += bias[i]; u += bias[inner + i]; }
+  act[(size_t)m * inner + i] = from_float<T>(gated_act(g, u, kind, limit, alpha));
+}
+
+}  // namespace nf
+
+extern "C" int nf_pair_hash_embed(const void* table, const int* ids, const int* row_seg, const int* seg_row0,
+                                  const int* seg_slot, int* last, long long slot_stride, float* h, int T, int hidden,
+                                  int buckets, long long mul_prev, long long mul_cur, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && hidden > 0 && buckets > 0 && mul_prev >= 0 && mul_cur >= 0, "pair_hash_embed: bad arguments");
+  if (dtype == kF32)
+    launch_chained(pair_hash_embed_kernel<float>, dim3(T), dim3(row_threads(hidden)), 0, stream, (const float*)table, ids, row_seg, seg_row0, seg_slot, last, (long)slot_stride, h, hidden, buckets, (unsigned long long)mul_prev, (unsigned long long)mul_cur);
+  else
+    launch_chained(pair_hash_embed_kernel<__nv_bfloat16>, dim3(T), dim3(row_threads(hidden)), 0, stream, (const __nv_bfloat16*)table, ids, row_seg, seg_row0, seg_slot, last, (long)slot_stride, h, hidden, buckets, (unsigned long long)mul_prev, (unsigned long long)mul_cur);
+  return check_launch("pair_hash_embed");
+}
+
+extern "C" int nf_gated_bias_act(const void* gu, int in_dtype, const float* bias, void* act, int M, int inner, int kind,
+                                 float limit, float alpha, int dtype, cudaStream_t stream) {
+  if (M == 0) return 0;
+  NF_REQUIRE(M > 0 && inner > 0 && M <= 65535 * 1024, "gated_bias_act: bad sizes M=%d inner=%d", M, inner);
+  NF_REQUIRE(kind == kActSilu || kind == kActCapped, "gated_bias_act: activation %d", kind);
+  NF_REQUIRE(in_dtype == kF32 || in_dtype == dtype, "gated_bias_act: the input is float32 or of the output's type");
+  // rows in grid.y, 65535 at a time
+  for (int m0 = 0; m0 < M; m0 += 65535) {
+    const int rows = M - m0 < 65535 ? M - m0 : 65535;
+    const dim3 grid((inner + 255) / 256, rows);
+    const size_t in_off = (size_t)m0 * 2 * inner, out_off = (size_t)m0 * inner;
+    if (dtype == kF32)
+      launch_chained(gated_bias_act_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)gu + in_off, bias, (float*)act + out_off, inner, kind, limit, alpha);
+    else if (in_dtype == kF32)
+      launch_chained(gated_bias_act_kernel<float, __nv_bfloat16>, grid, dim3(256), 0, stream, (const float*)gu + in_off, bias, (__nv_bfloat16*)act + out_off, inner, kind, limit, alpha);
+    else
+      launch_chained(gated_bias_act_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu + in_off, bias, (__nv_bfloat16*)act + out_off, inner, kind, limit, alpha);
+  }
+  return check_launch("gated_bias_act");
+}
+
+namespace nf {
+// out[i] = x[i] rounded to T (the stream's copy in the engine's type)
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, long long n) {
+  chain_wait(x);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = from_float<T>(x[i]);
+}
+}  // namespace nf
+
+extern "C" int nf_cast_rows(const float* x, void* out, long long n, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  NF_REQUIRE(n > 0 && dtype == kBF16, "cast_rows: float32 to bfloat16 only");
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  launch_chained(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, (__nv_bfloat16*)out, n);
+  return check_launch("cast_rows");
+}

@@ -19,7 +19,7 @@ template <typename TA, typename TC, bool SWIGLU>
 __global__ void __launch_bounds__(256)
 gemm_nt_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ B, size_t b_group_stride,
                TC* __restrict__ C, int ldc, int M, int N, int K,
-               const int* __restrict__ offsets, const int* __restrict__ a_rows, int a_div) {
+               const int* __restrict__ offsets, const int* __restrict__ a_rows, int a_div, GatedActParams act) {
   // N is the number of output columns (for SWIGLU: the inner width; B has 2N rows).
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
@@ -90,7 +90,7 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ B, size
         const int c = n0 + tx + 16 * j;
         if (c < N) {
           const float gt = acc[i][j], up = acc[i][j + 2];
-          C[(size_t)r * ldc + c] = from_float<TC>(gt / (1.f + expf(-gt)) * up);
+          C[(size_t)r * ldc + c] = from_float<TC>(gated_act(gt, up, act));
         }
       }
     } else {
@@ -106,14 +106,14 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ B, size
 template <typename TA, typename TC>
 static int launch(const void* A, int lda, const void* B, size_t bgs, void* C, int ldc, int M, int N,
                   int K, int groups, int max_rows_per_group, const int* offsets,
-                  const int* a_rows, int a_div, bool swiglu, cudaStream_t stream) {
+                  const int* a_rows, int a_div, bool swiglu, GatedActParams act, cudaStream_t stream) {
   const int ncol = swiglu ? BN / 2 : BN;
   dim3 grid((N + ncol - 1) / ncol, (max_rows_per_group + BM - 1) / BM, groups);
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm: too many row tiles (%u) or groups (%u)", grid.y, grid.z);
   if (swiglu)
-    gemm_nt_kernel<TA, TC, true><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)B, bgs, (TC*)C, ldc, M, N, K, offsets, a_rows, a_div);
+    gemm_nt_kernel<TA, TC, true><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)B, bgs, (TC*)C, ldc, M, N, K, offsets, a_rows, a_div, act);
   else
-    gemm_nt_kernel<TA, TC, false><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)B, bgs, (TC*)C, ldc, M, N, K, offsets, a_rows, a_div);
+    gemm_nt_kernel<TA, TC, false><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)B, bgs, (TC*)C, ldc, M, N, K, offsets, a_rows, a_div, act);
   return check_launch("gemm_simt");
 }
 
@@ -123,20 +123,23 @@ using namespace nf;
 
 // C[M, N] = epilogue(A[M, K] * B[g]^T).  in_dtype: A and B; out_dtype: C (float32 allowed
 // with bfloat16 inputs, for logits).  groups == 1 and offsets == null: dense.
-// For swiglu, B[g] has 2N rows (gate rows first) and C has N columns.
+// For swiglu (1: silu(gate) * up; 2: the capped form of common.cuh with act_limit, act_alpha),
+// B[g] has 2N rows (gate rows first) and C has N columns.
 extern "C" int nf_gemm_simt(const void* A, int lda, const void* B, long long b_group_stride, void* C,
                             int ldc, int M, int N, int K, int groups, int max_rows_per_group,
                             const int* offsets, const int* a_rows, int a_div, int swiglu,
-                            int in_dtype, int out_dtype, cudaStream_t stream) {
+                            int in_dtype, int out_dtype, float act_limit, float act_alpha, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && a_div > 0, "gemm: bad sizes M=%d N=%d K=%d groups=%d", M, N, K, groups);
   NF_REQUIRE(groups == 1 || offsets, "gemm: grouped product needs row offsets");
+  NF_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm: epilogue %d (0 none, 1 silu-gated, 2 capped)", swiglu);
+  const GatedActParams act{swiglu, act_limit, act_alpha};
   if (in_dtype == kF32 && out_dtype == kF32)
-    return launch<float, float>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu, stream);
+    return launch<float, float>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu != 0, act, stream);
   if (in_dtype == kBF16 && out_dtype == kBF16)
-    return launch<__nv_bfloat16, __nv_bfloat16>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu, stream);
+    return launch<__nv_bfloat16, __nv_bfloat16>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu != 0, act, stream);
   if (in_dtype == kBF16 && out_dtype == kF32)
-    return launch<__nv_bfloat16, float>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu, stream);
+    return launch<__nv_bfloat16, float>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu != 0, act, stream);
   set_error("gemm: unsupported dtype pair in=%d out=%d", in_dtype, out_dtype);
   return 1;
 }

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_constant__ CUtensorMap map_x,
                        const __grid_constant__ CUtensorMap map_x_half,
                        const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int ldo,
-                       int n_features, int K, int groups) {
+                       int n_features, int K, int groups, GatedActParams act) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   static_assert(!(SWIGLU && PAIR), "the first product already has two weight tiles an item");
@@ -289,8 +289,13 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
                   float v0 = __uint_as_float(g[c]), v1 = __uint_as_float(g[c + 1]);
                   // the result is rounded to bfloat16 (2^-9): the fast exponential's 2^-21 is far below
                   if (SWIGLU) {
-                    v0 = __fdividef(v0, 1.f + __expf(-v0)) * __uint_as_float(u[c]);
-                    v1 = __fdividef(v1, 1.f + __expf(-v1)) * __uint_as_float(u[c + 1]);
+                    if (act.kind == kActCapped) {
+                      v0 = gated_act(v0, __uint_as_float(u[c]), act);
+                      v1 = gated_act(v1, __uint_as_float(u[c + 1]), act);
+                    } else {
+                      v0 = __fdividef(v0, 1.f + __expf(-v0)) * __uint_as_float(u[c]);
+                      v1 = __fdividef(v1, 1.f + __expf(-v1)) * __uint_as_float(u[c + 1]);
+                    }
                   }
                   const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
                   pk[8 * j + c / 2] = *reinterpret_cast<const unsigned*>(&h);
@@ -328,7 +333,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
 
 template <bool SWIGLU, bool PAIR>
 static int launch_tc(const void* Wp, const CUtensorMap& mx, const CUtensorMap& mx_half, const int* offsets, void* out, int ldo,
-                     int n_features, int K, int groups, cudaStream_t stream) {
+                     int n_features, int K, int groups, GatedActParams act, cudaStream_t stream) {
   const size_t smem = (size_t)kSmemBudget + 1024;
   static bool set = false;
   if (!set) {
@@ -347,7 +352,7 @@ static int launch_tc(const void* Wp, const CUtensorMap& mx, const CUtensorMap& m
   // at least one pass per non-empty group; the kernel itself counts the exact number of items
   const int grid = n_sm;
   launch_chained(grouped_gemm_tc_kernel<SWIGLU, PAIR>, dim3(grid), dim3(kTcThreads), smem, stream,
-                 (const __nv_bfloat16*)Wp, mx, mx_half, offsets, (__nv_bfloat16*)out, ldo, n_features, K, groups);
+                 (const __nv_bfloat16*)Wp, mx, mx_half, offsets, (__nv_bfloat16*)out, ldo, n_features, K, groups, act);
   return check_launch("grouped_gemm_tc");
 }
 
@@ -374,7 +379,7 @@ extern "C" int nf_set_grouped_gemm_pair(int on, int min_rows) {
 // zero-padded.  Needs K % 8 == 0 and a 16-byte aligned X (TMA).
 extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const void* Wp, int groups,
                                   int n_features, int K, const int* offsets, void* out, int ldo,
-                                  int swiglu, cudaStream_t stream) {
+                                  int swiglu, float act_limit, float act_alpha, cudaStream_t stream) {
   if (total_rows == 0) return 0;
   NF_REQUIRE(total_rows > 0 && groups > 0 && n_features > 0 && K > 0, "grouped_gemm_tc: bad sizes");
   NF_REQUIRE(K % 8 == 0, "grouped_gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
@@ -383,12 +388,14 @@ extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const voi
   CUtensorMap mx, mx_half;
   if (int rc = make_map(&mx, X, total_rows, K, kXBox)) return rc;
   if (int rc = make_map(&mx_half, X, total_rows, K, kXBox / 2)) return rc;
-  if (swiglu) return launch_tc<true, false>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, stream);
+  NF_REQUIRE(swiglu >= 0 && swiglu <= 2, "grouped_gemm_tc: epilogue %d (0 none, 1 silu-gated, 2 capped)", swiglu);
+  const GatedActParams act{swiglu, act_limit, act_alpha};
+  if (swiglu) return launch_tc<true, false>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, act, stream);
   // two feature tiles an item once an expert's rows weigh about as much as a tile's weights
   // (decided by the counts the host knows: all rows, all groups)
   if (g_tc_pair && total_rows >= (long long)g_tc_pair_min_rows * groups)
-    return launch_tc<false, true>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, stream);
-  return launch_tc<false, false>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, stream);
+    return launch_tc<false, true>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, act, stream);
+  return launch_tc<false, false>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, act, stream);
 }
 
 // A wait that nothing will ever satisfy, given `polls` polls: the bounded wait runs out, records

@@ -102,6 +102,7 @@ struct MsArgs {
   const __nv_bfloat16* Ws13;   // packed [n_shared][...] like W13
   const __nv_bfloat16* Ws2;    // packed [n_shared][...] like W2
   long long gss13, gss2;
+  GatedActParams gated;        // the first product's gated epilogue
   float* cw;                   // [T, k + n_shared] weights of the k experts, then sigmoid(gate) (or 1) for every chunk
   int* cinv;                   // [T, k + n_shared] rows of Y that belong to them
   int n_shared;
@@ -740,7 +741,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
           const int r = 2 * t + (i & 1), f = f_lo + (i >> 1) * 8;
           if (r < rows && f < N) {
             float v = acc[0][i];
-            if (!item.second) v = v / (1.f + expf(-v)) * acc[1][i];
+            if (!item.second) v = gated_act(v, acc[1][i], p.gated);
             out[(size_t)(row_begin + r) * N + f] = __float2bfloat16_rn(v);
           }
         }
@@ -854,7 +855,7 @@ extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long 
                              int smem_bytes, const float* Wr, int extra, int norm_topk, float* logits, int* topk_idx,
                              float* topk_w, float* extra_out, int* inv, const void* Ws13, long long gss13,
                              const void* Ws2, long long gss2, int n_shared, float* cw, int* cinv,
-                             cudaStream_t stream) {
+                             int act_kind, float act_limit, float act_alpha, cudaStream_t stream) {
   if (M == 0) return 0;
   NF_REQUIRE(M > 0 && T > 0 && k > 0 && E > 0 && ldx % 8 == 0 && n_shared >= 0, "moe_stream: bad sizes");
   NF_REQUIRE(!Wr || (logits && topk_idx && topk_w && inv && extra >= 0 && (extra == 0 || extra_out) && M == T * k && k <= E),
@@ -867,7 +868,9 @@ extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long 
              H, I, M, n_mapped, q, smem_bytes, n_shared);
   NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W13 % 16 == 0) && ((uintptr_t)W2 % 16 == 0) && ((uintptr_t)act % 16 == 0) &&
              gs13 % 8 == 0 && gs2 % 8 == 0, "moe_stream: operands must be 16-byte aligned");
+  NF_REQUIRE(act_kind == kActSilu || act_kind == kActCapped, "moe_stream: gated epilogue %d", act_kind);
   MsArgs a;
+  a.gated = GatedActParams{act_kind, act_limit, act_alpha};
   a.X = (const __nv_bfloat16*)X; a.W13 = (const __nv_bfloat16*)W13; a.W2 = (const __nv_bfloat16*)W2;
   a.act = (__nv_bfloat16*)act; a.Y = (__nv_bfloat16*)Y;
   a.offsets = offsets; a.order = order; a.active = active; a.work = work;

@@ -243,3 +243,141 @@ extern "C" int nf_scale_gather_rows(const void* x, const int* order, int div, co
   }
   return check_launch("scale_gather_rows");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Norm on a sublayer's output: h[t] += ls * (d / rms(d)) * w with d = delta[t] (+ bias), and, if
+// `out`, out[t] = h[t] in the engine's type (the next sublayer's input).  delta may be float32 or
+// the engine's type; the sum, the mean of squares and the products are float32.
+// ---------------------------------------------------------------------------------------------
+namespace nf {
+
+template <typename TD, typename TO>
+__global__ void scaled_norm_add_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const float* __restrict__ bias, const float* __restrict__ w,
+                                       const float* __restrict__ ls, float eps, TO* __restrict__ out, int hidden) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  chain_release_if_small();
+  chain_wait(h, delta);
+  float* hr = h + (size_t)r * hidden;
+  const TD* dr = delta + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float d = to_float(dr[i]) + (bias ? bias[i] : 0.f);
+    ss += d * d;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float d = to_float(dr[i]) + (bias ? bias[i] : 0.f);
+    float v = d * inv * w[i];
+    if (ls) v *= ls[i];
+    v += hr[i];
+    hr[i] = v;
+    if (out) out[(size_t)r * hidden + i] = from_float<TO>(v);
+  }
+}
+
+// out[t] = (1 / n) * sum_m (x_m[t] / rms(x_m[t])) * w_m: the mean of several mixers' outputs, each
+// first over its own root mean square and times its own weight.  out is float32.
+struct NormedInputs {
+  const void* x[4];
+  const float* w[4];
+  int n;
+};
+
+template <typename T>
+__global__ void mean_of_rmsnorms_kernel(NormedInputs in, float eps, float* __restrict__ out, int hidden) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  chain_release_if_small();
+  chain_wait();
+  float inv[4];
+  for (int m = 0; m < in.n; ++m) {
+    const T* xr = reinterpret_cast<const T*>(in.x[m]) + (size_t)r * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = to_float(xr[i]);
+      ss += v * v;
+    }
+    inv[m] = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+  }
+  const float share = 1.f / (float)in.n;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float s = 0.f;
+    for (int m = 0; m < in.n; ++m)
+      s += to_float(reinterpret_cast<const T*>(in.x[m])[(size_t)r * hidden + i]) * inv[m] * in.w[m][i];
+    out[(size_t)r * hidden + i] = s * share;
+  }
+}
+
+// out[t, c] = y[t, c] / rms(part of c) * w[c] * act(z[t, zcol0 + c]): an RMS norm in `parts` equal
+// parts of a row (w null: no weight), then a gate.  act 0: silu, 1: sigmoid.  y is float32.
+template <typename T>
+__global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const T* __restrict__ zsrc, int ldz, int zcol0,
+                                          const float* __restrict__ w, float eps, T* __restrict__ out, int inner,
+                                          int parts, int act) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, part = blockIdx.y;
+  const int n = inner / parts, c0 = part * n;
+  chain_release_if_small();
+  chain_wait(y, zsrc);
+  const float* yr = y + (size_t)t * inner + c0;
+  const T* zr = zsrc + (size_t)t * ldz + zcol0 + c0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += yr[i] * yr[i];
+  const float inv = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  T* o = out + (size_t)t * inner + c0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float z = to_float(zr[i]);
+    const float sg = 1.f / (1.f + expf(-z));
+    const float gate = act == 1 ? sg : z * sg;
+    o[i] = from_float<T>(yr[i] * inv * (w ? w[c0 + i] : 1.f) * gate);
+  }
+}
+
+static inline int norm_threads(int n) {
+  int t = 32;
+  while (t < n && t < 512) t <<= 1;
+  return t;
+}
+
+}  // namespace nf
+
+// delta_dtype: 0 float32, 1 bfloat16; out (may be null) has out_dtype.
+extern "C" int nf_scaled_norm_add(float* h, const void* delta, int delta_dtype, const float* bias, const float* w,
+                                  const float* ls, float eps, void* out, int out_dtype, int R, int hidden,
+                                  cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && hidden > 0 && h && delta && w, "scaled_norm_add: bad arguments R=%d hidden=%d", R, hidden);
+  const dim3 grid(R), block(norm_threads(hidden));
+#define NF_SNA(TD, TO) \
+  launch_chained(scaled_norm_add_kernel<TD, TO>, grid, block, 0, stream, h, (const TD*)delta, bias, w, ls, eps, (TO*)out, hidden)
+  if (delta_dtype == kF32) { if (out_dtype == kF32) NF_SNA(float, float); else NF_SNA(float, __nv_bfloat16); }
+  else { if (out_dtype == kF32) NF_SNA(__nv_bfloat16, float); else NF_SNA(__nv_bfloat16, __nv_bfloat16); }
+#undef NF_SNA
+  return check_launch("scaled_norm_add");
+}
+
+extern "C" int nf_mean_of_rmsnorms(const void* const* xs, const float* const* ws, int n, float eps, float* out, int R,
+                                   int hidden, int dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(n >= 1 && n <= 4 && R > 0 && hidden > 0, "mean_of_rmsnorms: %d inputs (1 to 4), R=%d hidden=%d", n, R, hidden);
+  NormedInputs in;
+  in.n = n;
+  for (int m = 0; m < 4; ++m) { in.x[m] = m < n ? xs[m] : nullptr; in.w[m] = m < n ? ws[m] : nullptr; }
+  if (dtype == kF32) launch_chained(mean_of_rmsnorms_kernel<float>, dim3(R), dim3(norm_threads(hidden)), 0, stream, in, eps, out, hidden);
+  else launch_chained(mean_of_rmsnorms_kernel<__nv_bfloat16>, dim3(R), dim3(norm_threads(hidden)), 0, stream, in, eps, out, hidden);
+  return check_launch("mean_of_rmsnorms");
+}
+
+extern "C" int nf_group_rmsnorm_gate(const float* y, const void* z, int ldz, int zcol0, const float* w, float eps,
+                                     void* out, int R, int inner, int parts, int act, int dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && inner > 0 && parts > 0 && inner % parts == 0 && parts <= 65535,
+             "group_rmsnorm_gate: %d does not split into %d parts", inner, parts);
+  NF_REQUIRE(act == 0 || act == 1, "group_rmsnorm_gate: gate %d (0 silu, 1 sigmoid)", act);
+  const dim3 grid(R, parts), block(norm_threads(inner / parts));
+  if (dtype == kF32) launch_chained(group_rmsnorm_gate_kernel<float>, grid, block, 0, stream, y, (const float*)z, ldz, zcol0, w, eps, (float*)out, inner, parts, act);
+  else launch_chained(group_rmsnorm_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, y, (const __nv_bfloat16*)z, ldz, zcol0, w, eps, (__nv_bfloat16*)out, inner, parts, act);
+  return check_launch("group_rmsnorm_gate");
+}

@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? 4 : 3)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
                    const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div,
-                   const int* __restrict__ group_map, int early_index, int n_groups, RopeEpilogue rope, int ksplit) {
+                   const int* __restrict__ group_map, int early_index, int n_groups, RopeEpilogue rope, int ksplit,
+                   GatedActParams act) {
   // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
   // ksplit > 1: blockIdx.x counts (row tile, cluster member); member s takes the s-th part of k
   __shared__ float partial[kWarps][NT * 4 * 32];
@@ -330,7 +331,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
       }
     } else if (SWIGLU) {
       const int f = n0 + gg;
-      if (f < N) Y[(size_t)row * ldy + f] = from_float<TC>(lo / (1.f + expf(-lo)) * hi);
+      if (f < N) Y[(size_t)row * ldy + f] = from_float<TC>(gated_act(lo, hi, act));
     } else {
       const int f0 = n0 + gg, f1 = n0 + gg + 8;
       if (f0 < N) Y[(size_t)row * ldy + f0] = from_float<TC>(lo);
@@ -338,6 +339,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     }
   }
 }
+
+static thread_local GatedActParams t_gated_act{kActSilu, 0.f, 0.f};   // the current call's gated epilogue
 
 int g_skinny_max_split = kMaxSplit;      // nf_set_skinny_max_split(): 1 turns the split over k off
 
@@ -360,11 +363,11 @@ static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y,
     grid.x *= ksplit;
     launch_chained_cluster(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream, ksplit,
                            (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets,
-                           x_rows, x_div, group_map, early_index, groups, RopeEpilogue{}, ksplit);
+                           x_rows, x_div, group_map, early_index, groups, RopeEpilogue{}, ksplit, t_gated_act);
   } else {
     launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
-                   x_div, group_map, early_index, groups, RopeEpilogue{}, 1);
+                   x_div, group_map, early_index, groups, RopeEpilogue{}, 1, t_gated_act);
   }
   return check_launch("skinny_gemm");
 }
@@ -388,6 +391,7 @@ using namespace nf;
 // Y[M, N] = epilogue(X[M, K] W[g]^T), bfloat16 inputs, float32 accumulation.
 // out_dtype: 1 bfloat16, 0 float32.  max_rows: bound on the rows of any one group.
 // Needs K % 8 == 0 and 16-byte aligned rows (ldx % 8 == 0, bases aligned).
+// swiglu: 0 none, 1 silu(gate) * up, 2 the capped form of common.cuh (act_limit, act_alpha).
 // packed != 0: W is in the packed tile layout (w_group_stride then counts packed elements).
 // group_map / n_mapped: optional list of the groups to run (-1 entries are skipped); the grid
 // then has n_mapped groups instead of `groups`.  early_index != 0: offsets, x_rows and group_map
@@ -397,7 +401,7 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
                               int ldy, int M, int N, int K, int groups, int max_rows,
                               const int* offsets, const int* x_rows, int x_div, int swiglu,
                               int out_dtype, int packed, const int* group_map, int n_mapped,
-                              int early_index, cudaStream_t stream) {
+                              int early_index, float act_limit, float act_alpha, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && x_div > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   NF_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "skinny_gemm: K=%d and the row stride %d must be multiples of 8", K, ldx);
@@ -410,6 +414,8 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   const size_t wgs = (size_t)w_group_stride;
   if (swiglu) {
     NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");
+    NF_REQUIRE(swiglu == kActSilu || swiglu == kActCapped, "skinny_gemm: gated epilogue %d", swiglu);
+    t_gated_act = GatedActParams{swiglu, act_limit, act_alpha};
     return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
   }
   if (out_dtype == kBF16)
@@ -446,11 +452,11 @@ extern "C" int nf_skinny_qkv_rope(const void* X, int ldx, const void* W, void* Y
   if (M <= 8)
     launch_chained(skinny_gemm_kernel<1, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r, 1);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r, 1, GatedActParams{kActNone, 0.f, 0.f});
   else
     launch_chained(skinny_gemm_kernel<2, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r, 1);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r, 1, GatedActParams{kActNone, 0.f, 0.f});
   return check_launch("skinny_qkv_rope");
 }
 

@@ -131,6 +131,25 @@ def check_router_sizes(num_experts: int, top_k: int) -> None:
         raise ValueError(f"top_k={top_k} must lie in [1, {num_experts}]")
 
 
+# The gated activation of a feed-forward's first product: (kind, limit, alpha).  Kind 1 is
+# silu(gate) * up; kind 2 the capped form min(g, limit) * sigmoid(alpha * min(g, limit)) *
+# (clamp(up, -limit, limit) + 1).
+ACT_SILU = (1, 0.0, 0.0)
+
+
+def capped_activation(limit: float, alpha: float) -> Tuple[int, float, float]:
+    if not limit > 0:
+        raise ValueError(f"capped activation: limit={limit} must be positive")
+    return (2, float(limit), float(alpha))
+
+
+def _act(swiglu, act) -> Tuple[int, float, float]:
+    """The epilogue a product is launched with: none, or the gated activation `act`."""
+    if not swiglu:
+        return (0, 0.0, 0.0)
+    return ACT_SILU if act is None else act
+
+
 def _p(t: Optional[torch.Tensor]):
     return None if t is None else c_void_p(t.data_ptr())
 
@@ -202,21 +221,23 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------
 
 def _gemm_simt(a, lda, b, b_group_stride, c, M, N, K, groups, max_rows, offsets, a_rows, a_div,
-               swiglu) -> None:
+               swiglu, act=None) -> None:
+    kind, limit, alpha = _act(swiglu, act)
     _lib.call("nf_gemm_simt", _p(a), c_int(lda), _p(b), c_longlong(b_group_stride), _p(c),
               c_int(c.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
-              _p(offsets), _p(a_rows), c_int(a_div), c_int(1 if swiglu else 0), c_int(_dt(a)),
-              c_int(_dt(c)), _stream())
+              _p(offsets), _p(a_rows), c_int(a_div), c_int(kind), c_int(_dt(a)),
+              c_int(_dt(c)), c_float(limit), c_float(alpha), _stream())
 
 
 def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu,
-            packed=False, group_map=None, early_index=False) -> None:
+            packed=False, group_map=None, early_index=False, act=None) -> None:
+    kind, limit, alpha = _act(swiglu, act)
     _lib.call("nf_skinny_gemm", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
               c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
-              _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
+              _p(offsets), _p(x_rows), c_int(x_div), c_int(kind), c_int(_dt(out)),
               c_int(1 if packed else 0), _p(group_map),
               c_int(group_map.numel() if group_map is not None else 0), c_int(1 if early_index else 0),
-              _stream())
+              c_float(limit), c_float(alpha), _stream())
 
 
 class PackedWeights:
@@ -521,7 +542,56 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
     _lib.call("nf_paged_attention_generic", _p(qkv), c_int(qkv.shape[1]), _p(pages),
               _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg),
               _p(out), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
-              c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(_dt(qkv)), _stream())
+              c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(_dt(qkv)), None, c_int(0), None,
+              c_int(0), _stream())
+    return out
+
+
+def qk_whole_norm_append(proj: torch.Tensor, q_col0: int, k_col0: int, bias_q: Optional[torch.Tensor],
+                         bias_k: Optional[torch.Tensor], wq: torch.Tensor, wk: torch.Tensor, eps: float,
+                         Hq: int, Hkv: int, D: int, ctx, pages: torch.Tensor, block_table: torch.Tensor,
+                         page_size: int, append: bool) -> torch.Tensor:
+    """For an attention whose values are its keys.  proj float32 [T, ld] holds q (Hq x D) at q_col0
+    and k (Hkv x D) at k_col0.  Adds the biases; q and k each over the root mean square of their
+    whole row slice, times wq / wk; returns q [T, Hq * D] in the cache's type, and writes the normed
+    keys as keys and the biased, un-normed keys as values at (request, position)."""
+    _chk(proj, "proj", torch.float32); _chk(wq, "wq", torch.float32); _chk(wk, "wk", torch.float32)
+    _chk(block_table, "block_table", torch.int32); _chk(pages, "pages")
+    for b, n in ((bias_q, "bias_q"), (bias_k, "bias_k")):
+        if b is not None:
+            _chk(b, n, torch.float32)
+    T = proj.shape[0]
+    q = torch.empty((T, Hq * D), dtype=pages.dtype, device=proj.device)
+    _lib.call("nf_qk_whole_norm_append", _p(proj), c_int(proj.shape[1]), c_int(q_col0), c_int(k_col0), _p(bias_q),
+              _p(bias_k), _p(wq), _p(wk), c_float(eps), _p(ctx.positions), _p(ctx.row_seg), _p(q), c_int(T), c_int(Hq),
+              c_int(Hkv), c_int(D), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(page_size),
+              c_int(pages.shape[0]), c_int(1 if append else 0), c_int(_dt(pages)), _stream())
+    return q
+
+
+def biased_window_attention(q: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.Tensor, block_table: torch.Tensor,
+                            page_size: int, ctx, window: int, keep_first: int, scale: float,
+                            slopes: Optional[torch.Tensor], gate: Optional[torch.Tensor] = None,
+                            gate_col0: int = 0) -> torch.Tensor:
+    """Causal softmax attention of q [T, Hq * D] over the paged keys and values -> [T, Hq * D], with
+    slopes[h] * (i - j) taken off head h's score of key j (float32 [Hq] or None), a window (0: none) that
+    keeps the request's first `keep_first` keys visible, and head h's output times
+    sigmoid(gate[t, gate_col0 + h]) (gate float32 [T, ld] or None)."""
+    _chk(q, "q"); _chk(pages, "pages", q.dtype); _chk(block_table, "block_table", torch.int32)
+    if slopes is not None:
+        _chk(slopes, "slopes", torch.float32)
+    if gate is not None:
+        _chk(gate, "gate", torch.float32)
+    T = q.shape[0]
+    out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+    if T == 0:
+        return out
+    gate_p = c_void_p(gate.data_ptr() + 4 * gate_col0) if gate is not None else None
+    _lib.call("nf_paged_attention_generic", _p(q), c_int(q.shape[1]), _p(pages), _p(block_table),
+              c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out), c_int(T), c_int(Hq),
+              c_int(Hkv), c_int(D), c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale),
+              c_int(_dt(q)), _p(slopes), c_int(keep_first if window > 0 else 0), gate_p,
+              c_int(gate.shape[1] if gate is not None else 0), _stream())
     return out
 
 
@@ -671,7 +741,7 @@ def moe_gather(x: torch.Tensor, plan: MoePlan, k: int) -> torch.Tensor:
 
 
 def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[torch.Tensor] = None,
-              sorted_rows: bool = False) -> torch.Tensor:
+              sorted_rows: bool = False, act=None) -> torch.Tensor:
     """Sorted pair p (token order[p] // k, expert e) -> silu(x Wgate_e^T) * (x Wup_e^T)  [T*k, I].
 
     `w13` is [E, 2I, H] (gate rows first), or `PackedWeights` of it for the bfloat16 kernels.
@@ -695,32 +765,34 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[to
         _chk(w13, "w13", x.dtype)
         E, two_i, _ = w13.shape
         inner = two_i // 2
-    act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
+    out = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
     if T == 0:
-        return act
+        return out
     if packed:
         if T <= TUNING["skinny_moe_max_tokens"]:
-            _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, rows,
-                    div, True, packed=True, group_map=plan.active)
+            _skinny(x, H, w13.data, w13.group_stride, out, T * k, inner, H, E, T, plan.offsets, rows,
+                    div, True, packed=True, group_map=plan.active, act=act)
         else:
             # rows in sorted order, then one tensor-core launch over all experts
             xp = gathered if gathered is not None else moe_gather(x, plan, k)
+            kind, limit, alpha = _act(True, act)
             _lib.call("nf_grouped_gemm_tc", _p(xp), c_longlong(T * k), _p(w13.data), c_int(E),
-                      c_int(inner), c_int(H), _p(plan.offsets), _p(act), c_int(inner), c_int(1), _stream())
-        return act
+                      c_int(inner), c_int(H), _p(plan.offsets), _p(out), c_int(inner), c_int(kind),
+                      c_float(limit), c_float(alpha), _stream())
+        return out
     path = "simt" if x.dtype == torch.float32 else _bf16_path(T, H, "bf16_moe")
     if path == "skinny":
-        _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, rows, div, True,
-                group_map=plan.active)
+        _skinny(x, H, w13, two_i * H, out, T * k, inner, H, E, T, plan.offsets, rows, div, True,
+                group_map=plan.active, act=act)
     else:
-        _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, rows, div, True)
-    return act
+        _gemm_simt(x, H, w13, two_i * H, out, T * k, inner, H, E, T, plan.offsets, rows, div, True, act=act)
+    return out
 
 
-def moe_experts_sorted(xs: torch.Tensor, w13, w2, plan: MoePlan) -> torch.Tensor:
+def moe_experts_sorted(xs: torch.Tensor, w13, w2, plan: MoePlan, act=None) -> torch.Tensor:
     """Both products of the routed experts over rows that are already in the experts' order
     (row p of `xs` is sorted pair p's input) -> [T*k, H] in the same order."""
-    return moe_gemm2(moe_gemm1(xs, w13, plan, plan.top_k, sorted_rows=True), w2, plan, plan_is_older=True)
+    return moe_gemm2(moe_gemm1(xs, w13, plan, plan.top_k, sorted_rows=True, act=act), w2, plan, plan_is_older=True)
 
 
 def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False) -> torch.Tensor:
@@ -748,7 +820,7 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
                     None, 1, False, packed=True, group_map=plan.active, early_index=plan_is_older)
         else:
             _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2.data), c_int(E), c_int(H),
-                      c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())
+                      c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), c_float(0.0), c_float(0.0), _stream())
         return y
     path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
     if path == "skinny":
@@ -801,7 +873,7 @@ def _stream_work(device: torch.device) -> torch.Tensor:
 
 
 def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
-                gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
+                gathered: Optional[torch.Tensor] = None, act=None) -> torch.Tensor:
     """Both products of the routed experts: sorted pair p of expert e ->
     (silu(x Wgate_e^T) * (x Wup_e^T)) Wdown_e^T  [T*k, H].
 
@@ -810,9 +882,10 @@ def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
     by `moe_gemm2`."""
     q = _stream_items(x, w13, w2, plan.num_experts, k) if plan.active is not None else 0
     if not q:
-        return moe_gemm2(moe_gemm1(x, w13, plan, k, gathered=gathered), w2, plan, plan_is_older=True)
+        return moe_gemm2(moe_gemm1(x, w13, plan, k, gathered=gathered, act=act), w2, plan, plan_is_older=True)
     T, H = x.shape
     inner = w13.n_features
+    kind, limit, alpha = _act(True, act)
     act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
     y = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
     _lib.call("nf_moe_stream", _p(x), c_int(x.stride(0)), _p(w13.data), c_longlong(w13.group_stride), _p(w2.data),
@@ -820,7 +893,8 @@ def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
               c_int(w13.groups), c_int(k), _p(plan.offsets), _p(plan.order), _p(plan.active),
               c_int(plan.active.numel()), _p(_stream_work(x.device)), c_int(q),
               c_int(TUNING["moe_stream_smem_kb"] * 1024), None, c_int(0), c_int(0), None, None, None, None, None,
-              None, c_longlong(0), None, c_longlong(0), c_int(0), None, None, _stream())
+              None, c_longlong(0), None, c_longlong(0), c_int(0), None, None, c_int(kind), c_float(limit),
+              c_float(alpha), _stream())
     return y
 
 
@@ -861,7 +935,7 @@ def can_route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, w13, w2, 
 
 
 def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool, w13, w2,
-                          shared: Optional[Tuple[PackedWeights, PackedWeights]] = None):
+                          shared: Optional[Tuple[PackedWeights, PackedWeights]] = None, act=None):
     """`route` and `moe_experts` in the one persistent launch: its CTAs compute the router logits
     between them, the one that finishes last selects and writes the plan, and all go on to the
     experts' products.  Returns (idx, weights, extra, plan, y) as the two calls would.
@@ -889,6 +963,7 @@ def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: in
     order = torch.empty((T * k,), dtype=torch.int32, device=dev)
     inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
     active = torch.empty((min(E, T * k),), dtype=torch.int32, device=dev)
+    kind, limit, alpha = _act(True, act)
     act = torch.empty((rows, inner), dtype=x.dtype, device=dev)
     y = torch.empty((rows, H), dtype=x.dtype, device=dev)
     cw = torch.empty((T, k + chunks), dtype=torch.float32, device=dev) if chunks else None
@@ -901,7 +976,7 @@ def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: in
               c_int(extra), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(inv),
               _p(s13.data) if chunks else None, c_longlong(s13.group_stride if chunks else 0),
               _p(s2.data) if chunks else None, c_longlong(s2.group_stride if chunks else 0), c_int(chunks),
-              _p(cw), _p(cinv), _stream())
+              _p(cw), _p(cinv), c_int(kind), c_float(limit), c_float(alpha), _stream())
     plan = MoePlan(offsets, order, inv, E, T, k, active)
     if not chunks:
         return idx, wts, ext, plan, y
@@ -1031,6 +1106,116 @@ def heads_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     batched product; float32 operands are multiplied in true float32)."""
     _chk(x, "x", contiguous=False); _chk(w, "w", x.dtype, contiguous=False)
     return torch.bmm(x, w)
+
+
+def scaled_norm_add(h: torch.Tensor, delta: torch.Tensor, bias: Optional[torch.Tensor], weight: torch.Tensor,
+                    scale: Optional[torch.Tensor], eps: float, out_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """h += scale * ((delta + bias) / rms(delta + bias)) * weight, float32 and in place; delta is float32 or
+    bfloat16.  With `out_dtype`, also returns the updated rows in that type (the next sublayer's input)."""
+    _chk(h, "h", torch.float32); _chk(delta, "delta"); _chk(weight, "weight", torch.float32)
+    for t, n in ((bias, "bias"), (scale, "scale")):
+        if t is not None:
+            _chk(t, n, torch.float32)
+    if delta.shape != h.shape:
+        raise ValueError("scaled_norm_add: delta does not have the stream's shape")
+    out = torch.empty(h.shape, dtype=out_dtype, device=h.device) if out_dtype is not None else None
+    _lib.call("nf_scaled_norm_add", _p(h), _p(delta), c_int(_dt(delta)), _p(bias), _p(weight), _p(scale), c_float(eps),
+              _p(out), c_int(_dt(out) if out is not None else 0), c_int(h.shape[0]), c_int(h.shape[1]), _stream())
+    return out
+
+
+def mean_of_rmsnorms(xs, ws, eps: float) -> torch.Tensor:
+    """float32 [T, W]: the mean over m of (xs[m] / rms(xs[m])) * ws[m]; one to four inputs of equal shape."""
+    n = len(xs)
+    if not 1 <= n <= 4 or len(ws) != n:
+        raise ValueError("mean_of_rmsnorms: one to four inputs, a weight each")
+    for x in xs:
+        _chk(x, "x", xs[0].dtype)
+        if x.shape != xs[0].shape:
+            raise ValueError("mean_of_rmsnorms: inputs of different shapes")
+    for w in ws:
+        _chk(w, "w", torch.float32)
+    T, W = xs[0].shape
+    out = torch.empty((T, W), dtype=torch.float32, device=xs[0].device)
+    xp = (c_void_p * n)(*[x.data_ptr() for x in xs])
+    wp = (c_void_p * n)(*[w.data_ptr() for w in ws])
+    _lib.call("nf_mean_of_rmsnorms", xp, wp, c_int(n), c_float(eps), _p(out), c_int(T), c_int(W), c_int(_dt(xs[0])),
+              _stream())
+    return out
+
+
+GATE_SILU, GATE_SIGMOID = 0, 1
+
+
+def group_rmsnorm_gate(y: torch.Tensor, z_src: torch.Tensor, z_col0: int, weight: Optional[torch.Tensor], eps: float,
+                       parts: int, gate: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Every one of `parts` equal parts of a row of y (float32 [T, inner]) over its own root mean square, times
+    `weight` (or nothing), times silu or sigmoid of z = z_src[:, z_col0 : z_col0 + inner] -> [T, inner]."""
+    _chk(y, "y", torch.float32); _chk(z_src, "z_src", out_dtype)
+    if weight is not None:
+        _chk(weight, "weight", torch.float32)
+    T, inner = y.shape
+    out = torch.empty((T, inner), dtype=out_dtype, device=y.device)
+    _lib.call("nf_group_rmsnorm_gate", _p(y), _p(z_src), c_int(z_src.shape[1]), c_int(z_col0), _p(weight), c_float(eps),
+              _p(out), c_int(T), c_int(inner), c_int(parts), c_int(gate), c_int(_dt(out)), _stream())
+    return out
+
+
+def gated_bias_act(gu: torch.Tensor, bias: Optional[torch.Tensor], act, out_dtype: torch.dtype) -> torch.Tensor:
+    """[M, 2I] (gate columns first; float32 or `out_dtype`) -> the gated activation `act` of (gate + bias, up + bias)."""
+    _chk(gu, "gu")
+    if bias is not None:
+        _chk(bias, "bias", torch.float32)
+    M, two_i = gu.shape
+    kind, limit, alpha = _act(True, act)
+    out = torch.empty((M, two_i // 2), dtype=out_dtype, device=gu.device)
+    _lib.call("nf_gated_bias_act", _p(gu), c_int(_dt(gu)), _p(bias), _p(out), c_int(M), c_int(two_i // 2), c_int(kind),
+              c_float(limit), c_float(alpha), c_int(_dt(out)), _stream())
+    return out
+
+
+def cast_rows(h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 stream rounded to the engine's type."""
+    _chk(h, "h", torch.float32)
+    out = torch.empty(h.shape, dtype=dtype, device=h.device)
+    _lib.call("nf_cast_rows", _p(h), _p(out), c_longlong(h.numel()), c_int(_dt(out)), _stream())
+    return out
+
+
+def pair_hash_embed(table: torch.Tensor, ctx, last: torch.Tensor, h: torch.Tensor, buckets: int, mul_prev: int,
+                    mul_cur: int) -> None:
+    """h[t] += table[(prev * mul_prev + token * mul_cur) mod buckets], or table[buckets] for a request's first
+    token.  `last` int32 [slots, 1]: each request's last token + 1 (0: none), read for a segment's first row and
+    updated to the segment's last token."""
+    _chk(table, "table"); _chk(h, "h", torch.float32); _chk(last, "last", torch.int32)
+    if table.shape[0] != buckets + 1 or table.shape[1] != h.shape[1]:
+        raise ValueError("pair_hash_embed: the table must be [buckets + 1, width]")
+    _lib.call("nf_pair_hash_embed", _p(table), _p(ctx.token_ids), _p(ctx.row_seg), _p(ctx.seg_row0), _p(ctx.seg_slot),
+              _p(last), c_longlong(last.stride(0)), _p(h), c_int(h.shape[0]), c_int(h.shape[1]), c_int(buckets),
+              c_longlong(mul_prev), c_longlong(mul_cur), c_int(_dt(table)), _stream())
+
+
+LINEAR_ATTENTION_MAX_DIM = 256
+
+
+def decay_linear_attention(src: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, decay: torch.Tensor,
+                           inv_freq: Optional[torch.Tensor], rot: int, k_scale: float, silu: bool,
+                           state: torch.Tensor, ctx, heads: int, D: int, V: int) -> torch.Tensor:
+    """The recurrence S <- decay_h S + k v^T, o = S^T q over a step's rows, request by request, from and into
+    each request's state (float32 [slots, heads * V * D], a column's D entries contiguous).  q, k (heads x D) and
+    v (heads x V) are columns of `src`; `silu` passes all three through SiLU first; the first `rot` dimensions of
+    every q and k head are turned by the row's position (inv_freq float32 [rot / 2]); k is scaled by `k_scale`.
+    Returns o float32 [T, heads * V]."""
+    _chk(src, "src"); _chk(decay, "decay", torch.float32); _chk(state, "state", torch.float32)
+    if rot:
+        _chk(inv_freq, "inv_freq", torch.float32)
+    T = src.shape[0]
+    out = torch.empty((T, heads * V), dtype=torch.float32, device=src.device)
+    _lib.call("nf_decay_linear_attention", _p(src), c_int(src.shape[1]), c_int(q_col0), c_int(k_col0), c_int(v_col0),
+              _p(decay), _p(inv_freq) if rot else None, c_int(rot), c_float(k_scale), c_int(1 if silu else 0),
+              _p(state), c_longlong(state.stride(0)), _p(ctx.seg_row0), _p(ctx.seg_slot), _p(ctx.seg_pos0), _p(out),
+              c_int(ctx.S), c_int(heads), c_int(D), c_int(V), c_int(_dt(src)), _stream())
+    return out
 
 
 # ---------------------------------------------------------------------------------------

@@ -53,7 +53,8 @@ class CacheSpec:
 
     kind "full": every entry stays until the request ends.
     kind "window": only the last `window` entries are read; pages that the window has
-    passed go back to the pool.
+    passed go back to the pool.  With `keep_first`, a request's first `keep_first` entries stay
+    readable however far the window has moved: the pages that hold them are never given back.
 
     The usual form is keys and values of `num_kv_heads` heads of `head_dim`: a page is
     ``[2, num_kv_heads, page_size, head_dim]`` (keys, then values; one head's keys of a page are
@@ -67,6 +68,7 @@ class CacheSpec:
     head_dim: int = 0
     window: Optional[int] = None
     row_width: int = 0
+    keep_first: int = 0
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         if self.row_width:
@@ -77,7 +79,7 @@ class CacheSpec:
         return self.row_width if self.row_width else 2 * self.num_kv_heads * self.head_dim
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.row_width)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.row_width, self.keep_first)
 
 
 @dataclass(frozen=True)
@@ -292,8 +294,29 @@ class RoutedSum:
         return kernels.moe_combine(self.y, self.plan, wts, self.shared, self.gate, self.dtype)
 
 
+@dataclass
+class StreamCopy:
+    """What a block that adds its sublayers' outputs to the stream itself leaves "pending": nothing
+    is left to add, and `x` is the stream as it stands, in the engine's type (None in 32-bit mode,
+    where the stream itself serves) - the next such block's input, saved a pass over the stream."""
+    x: Optional[torch.Tensor]
+
+
+@dataclass
+class BiasedOutput:
+    """A sublayer's output whose bias has not been added yet: `y` [T, hidden] (float32 sums or the
+    engine's type) and `bias` float32 [hidden].  A consumer that reads the rows anyway (the norm
+    on a sublayer's output) adds the bias in its own pass; anything else calls `summed()`."""
+    y: torch.Tensor
+    bias: torch.Tensor
+
+
 def summed(delta):
-    """`delta` as a tensor (None stays None)."""
+    """`delta` as a tensor (None stays None; a `StreamCopy` means nothing is left to add)."""
+    if isinstance(delta, StreamCopy):
+        return None
+    if isinstance(delta, BiasedOutput):
+        return delta.y + delta.bias.to(delta.y.dtype)
     return delta.materialize() if isinstance(delta, RoutedSum) else delta
 
 
@@ -329,6 +352,19 @@ class PositionEncoding(Part):
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
         """Encode in place: q [T, heads, D], k [T, kv_heads, D], positions int32 [T]."""
+        raise NotImplementedError
+
+
+class EmbeddingExtra(Part):
+    """Something added to the token embedding before the first layer (a second table looked up by
+    a hash of neighbouring tokens, for instance).  It may keep a small state per request."""
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def add(self, h: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor]) -> None:
+        """Add this part's rows to the float32 stream `h` [T, hidden] in place.  `state` is the
+        slab [slots, *state_spec.shape] indexed by `ctx.seg_slot`, zero for a new request."""
         raise NotImplementedError
 
 

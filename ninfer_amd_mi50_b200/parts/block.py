@@ -14,7 +14,7 @@ from typing import List, Optional
 import torch
 
 from ..registry import register_part
-from .base import Block, CacheView, FeedForward, Fetch, Mixer, Norm, StepContext, TensorSpec, summed
+from .base import Block, CacheView, FeedForward, Fetch, Mixer, Norm, RoutedSum, StepContext, TensorSpec, summed
 
 
 @register_part("block", "pre_norm")
@@ -48,7 +48,7 @@ class PreNormBlock(Block):
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: Optional[CacheView], state: Optional[torch.Tensor]
                 ) -> Optional[torch.Tensor]:
-        if not self.norm1.takes_unsummed:
+        if not self.norm1.takes_unsummed or not isinstance(pending, (torch.Tensor, RoutedSum, type(None))):
             pending = summed(pending)
         x1 = self.norm1.add_norm(h, pending, ctx.dtype)
         a = self.mixer.forward(x1, ctx, cache, state)
@@ -56,3 +56,81 @@ class PreNormBlock(Block):
             return a                                    # the mixer's output is what is left pending
         x2 = self.norm2.add_norm(h, a, ctx.dtype)
         return self.feed_forward.forward(x2, ctx)
+
+
+@register_part("block", "sublayer_norm_scaled")
+class SublayerNormScaledBlock(Block):
+    """The norm sits on each sublayer's output, and a learned vector scales it per channel:
+
+        h += scale1 * norm1(mixer(h));   h += scale2 * norm2(feed_forward(h))
+
+    The sublayers read the stream itself.  In bfloat16 mode they read its rounding, which the
+    kernel that adds a sublayer's output writes beside the float32 stream (`StreamCopy`), so the
+    stream is not read again for it.  Nothing is left pending: each sum happens at once, in the
+    same kernel as the norm and the scale.  A layer whose feed-forward is ``"none"`` has the first
+    line only.
+    """
+
+    wants_spec = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward, spec=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        names = dict(spec.names) if spec is not None else {}
+        prefix = spec.prefix if spec is not None else ""
+        self.width = norm1.size
+        self.scale_names = (prefix + names.get("scale1", "scale1"), prefix + names.get("scale2", "scale2"))
+        self.scale1 = self.scale2 = None
+
+    @property
+    def has_ff(self) -> bool:
+        return not getattr(self.feed_forward, "absent", False)
+
+    def parts(self):
+        return (self.norm1, self.mixer, self.norm2, self.feed_forward) if self.has_ff else (self.norm1, self.mixer)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.parts())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [s for p in self.parts() for s in p.tensor_specs()]
+        for name in self.scale_names[:2 if self.has_ff else 1]:
+            specs.append(TensorSpec(name, (self.width,), role="vector", init="norm"))
+        return specs
+
+    def load(self, fetch: Fetch) -> None:
+        for p in self.parts():
+            p.load(fetch)
+        self.scale1 = fetch(self.scale_names[0])
+        self.scale2 = fetch(self.scale_names[1]) if self.has_ff else None
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in self.parts()) + 4 * self.width * (2 if self.has_ff else 1)
+
+    def check_limits(self, dtype, max_context, page_size) -> None:
+        for p in self.parts():
+            p.check_limits(dtype, max_context, page_size)
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, cache: Optional[CacheView],
+                state: Optional[torch.Tensor]):
+        from .. import kernels
+        from .base import BiasedOutput, StreamCopy
+        copy_dtype = None if ctx.dtype == torch.float32 else ctx.dtype       # 32-bit mode reads the stream itself
+        if isinstance(pending, StreamCopy):
+            x = pending.x
+        else:
+            delta = summed(pending)                  # another arrangement ran before: add what it left
+            if delta is not None:
+                h.add_(delta.to(torch.float32))
+            x = None
+        if x is None:
+            x = h if copy_dtype is None else kernels.cast_rows(h, copy_dtype)
+        a = self.mixer.forward(x, ctx, cache, state)
+        x = self.norm1.add_scaled_norm(h, a, self.scale1, copy_dtype)
+        if self.has_ff:
+            f = self.feed_forward.forward(h if copy_dtype is None else x, ctx)
+            bias = None
+            if isinstance(f, BiasedOutput):          # the norm's kernel adds the bias in its own pass
+                f, bias = f.y, f.bias
+            x = self.norm2.add_scaled_norm(h, summed(f), self.scale2, copy_dtype, bias=bias)
+        return StreamCopy(x)

@@ -22,7 +22,19 @@ import torch
 
 from .. import kernels
 from ..registry import register_part
-from .base import FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
+from .base import BiasedOutput, FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
+
+
+def gated_activation(spec):
+    """A feed-forward's gated activation from its description: None or ("silu",) is silu(gate) * up;
+    ("capped", limit, alpha) is g' * sigmoid(alpha g') * (u' + 1) with g' = min(gate, limit) and
+    u' = clamp(up, -limit, limit)."""
+    if spec is None or tuple(spec) == ("silu",):
+        return None
+    spec = tuple(spec)
+    if len(spec) == 3 and spec[0] == "capped":
+        return kernels.capped_activation(float(spec[1]), float(spec[2]))
+    raise ValueError(f"unknown gated activation {spec!r}")
 
 
 _SIDE_STREAMS = {}
@@ -53,28 +65,50 @@ class NoFeedForward(FeedForward):
 class DenseSwiglu(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str):
+    DEFAULT_NAMES = (("gate", "gate_proj.weight"), ("up", "up_proj.weight"), ("down", "down_proj.weight"),
+                     ("gate_bias", "gate_proj.bias"), ("up_bias", "up_proj.bias"), ("down_bias", "down_proj.bias"))
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, activation=None, bias: bool = False,
+                 tensor_names=None):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.prefix = prefix
-        self.w_gate_up = self.w_down = None
+        self.activation, self.has_bias = gated_activation(activation), bool(bias)
+        self.names = dict(self.DEFAULT_NAMES)
+        self.names.update(dict(tensor_names or ()))
+        self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
+
+    def _n(self, what: str) -> str:
+        return self.prefix + self.names[what]
 
     def tensor_specs(self) -> List[TensorSpec]:
-        p, H, I = self.prefix, self.hidden_size, self.intermediate_size
-        return [TensorSpec(p + "gate_proj.weight", (I, H)),
-                TensorSpec(p + "up_proj.weight", (I, H)),
-                TensorSpec(p + "down_proj.weight", (H, I))]
+        H, I = self.hidden_size, self.intermediate_size
+        specs = [TensorSpec(self._n("gate"), (I, H)), TensorSpec(self._n("up"), (I, H)),
+                 TensorSpec(self._n("down"), (H, I))]
+        if self.has_bias:
+            specs += [TensorSpec(self._n("gate_bias"), (I,), role="vector"),
+                      TensorSpec(self._n("up_bias"), (I,), role="vector"),
+                      TensorSpec(self._n("down_bias"), (H,), role="vector")]
+        return specs
 
     def load(self, fetch: Fetch) -> None:
-        p = self.prefix
-        self.w_gate_up = torch.cat([fetch(p + "gate_proj.weight"), fetch(p + "up_proj.weight")],
-                                   dim=0).contiguous()
-        self.w_down = fetch(p + "down_proj.weight")
+        self.w_gate_up = torch.cat([fetch(self._n("gate")), fetch(self._n("up"))], dim=0).contiguous()
+        self.w_down = fetch(self._n("down"))
+        if self.has_bias:
+            self.b_gate_up = torch.cat([fetch(self._n("gate_bias")), fetch(self._n("up_bias"))]).contiguous()
+            self.b_down = fetch(self._n("down_bias"))
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up), self.w_down)
+    def forward(self, x: torch.Tensor, ctx: StepContext):
+        if not self.has_bias and self.activation is None:
+            return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up), self.w_down)
+        # biases (or another activation): both products hand on their float32 sums, so that a bias
+        # meets an unrounded value; the second bias is left to whoever reads the output next
+        gu = kernels.linear(x, self.w_gate_up, out_dtype=torch.float32)
+        act = kernels.gated_bias_act(gu, self.b_gate_up, self.activation, x.dtype)
+        y = kernels.linear(act, self.w_down, out_dtype=torch.float32)
+        return BiasedOutput(y, self.b_down) if self.has_bias else y
 
 
 @register_part("feed_forward", "sparse_moe_swiglu")
@@ -90,7 +124,10 @@ class SparseMoeSwiglu(FeedForward):
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, norm_topk_prob: bool,
                  moe_intermediate_size: int, shared_intermediate_size: int, prefix: str,
-                 scoring: str = "softmax", weight_on: str = "output", tensor_names=None):
+                 scoring: str = "softmax", weight_on: str = "output", tensor_names=None, activation=None):
+        self.activation = gated_activation(activation)
+        if self.activation is not None and shared_intermediate_size > 0:
+            raise ValueError("a shared expert is served with the silu-gated activation only")
         if not 1 <= top_k <= num_experts:
             raise ValueError(f"top_k={top_k} must lie in [1, num_experts={num_experts}]")
         if scoring not in ("softmax", "sigmoid"):
@@ -200,7 +237,7 @@ class SparseMoeSwiglu(FeedForward):
                 and kernels.can_route_and_run_experts(x, self.w_router, self.w13, self.w2, E, k, shared=self.ws_packed)):
             # a decode step: routing, the experts' products and the shared expert's are one persistent launch
             idx, wts, gate, plan, y, sum_wts, sum_plan = kernels.route_and_run_experts(
-                x, self.w_router, E, k, self.norm_topk_prob, self.w13, self.w2, shared=self.ws_packed)
+                x, self.w_router, E, k, self.norm_topk_prob, self.w13, self.w2, shared=self.ws_packed, act=self.activation)
             if SparseMoeSwiglu.record_routing is not None:
                 SparseMoeSwiglu.record_routing.append(idx.clone())
             return RoutedSum(y, sum_plan, sum_wts, None, None, x.dtype)
@@ -250,7 +287,7 @@ class SparseMoeSwiglu(FeedForward):
             kernels.chain_break()
         elif fused:
             idx, wts, gate, plan, y = kernels.route_and_run_experts(x, self.w_router, E, k, self.norm_topk_prob,
-                                                                    self.w13, self.w2)
+                                                                    self.w13, self.w2, act=self.activation)
         else:
             idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
                                                  split=self.w_router_split)
@@ -259,7 +296,7 @@ class SparseMoeSwiglu(FeedForward):
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
         if y is None:
-            y = kernels.moe_experts(x, self.w13, self.w2, plan, k, gathered=gathered)
+            y = kernels.moe_experts(x, self.w13, self.w2, plan, k, gathered=gathered, act=self.activation)
         if fork:
             main.wait_stream(side)
             kernels.chain_break()           # the kernel that adds up also reads what the other stream produced
@@ -281,10 +318,11 @@ class SparseMoeSwiglu(FeedForward):
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
         if self.weight_on == "input":
-            y = kernels.moe_experts_sorted(kernels.scale_gather_rows(x, plan, k, wts), self.w13, self.w2, plan)
+            y = kernels.moe_experts_sorted(kernels.scale_gather_rows(x, plan, k, wts), self.w13, self.w2, plan,
+                                           act=self.activation)
             wts = None                          # the weights are spent: the sum adds the outputs as they are
         else:
-            y = kernels.moe_experts(x, self.w13, self.w2, plan, k)
+            y = kernels.moe_experts(x, self.w13, self.w2, plan, k, act=self.activation)
         shared = None
         if self.has_shared:
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)

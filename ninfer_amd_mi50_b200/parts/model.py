@@ -17,7 +17,7 @@ import torch
 from .. import kernels
 from ..config.model_config import LayerCall, ModelPlan
 from ..registry import build_part, part_class
-from .base import CacheSpec, CacheView, Fetch, StateSpec, StepContext, TensorSpec, summed
+from .base import CacheSpec, CacheView, Fetch, RoutedSum, StateSpec, StepContext, TensorSpec, summed
 
 
 class DecoderModel:
@@ -30,7 +30,11 @@ class DecoderModel:
             mixer = build_part("mixer", spec.mixer, prefix=spec.name_of("mixer"))
             norm2 = build_part("norm", spec.norm, prefix=spec.name_of("norm2"))
             ffn = build_part("feed_forward", spec.feed_forward, prefix=spec.name_of("feed_forward"))
-            self.blocks.append(part_class("block", spec.arrangement)(norm1, mixer, norm2, ffn))
+            block_cls = part_class("block", spec.arrangement)
+            # an arrangement with tensors of its own (a layer scale, say) is told the layer's names
+            extra = {"spec": spec} if getattr(block_cls, "wants_spec", False) else {}
+            self.blocks.append(block_cls(norm1, mixer, norm2, ffn, **extra))
+        self.embedding_extras = [build_part("embedding", e) for e in plan.embedding_extras]
         self.final_norm = build_part("norm", plan.final_norm, prefix=plan.final_norm_name)
         self.order: List[LayerCall] = list(plan.order)
         vectors = dict(plan.stream_vectors)
@@ -44,6 +48,11 @@ class DecoderModel:
         # layer a slot of its own per call names more
         self.num_cache_slots = max([len(self.blocks)] + [c.cache + 1 for c in self.order])
         self.num_state_slots = max([len(self.blocks)] + [c.state_slot() + 1 for c in self.order])
+        # what the embedding's extras keep per request lives in state slots after the layers'
+        self.extra_state_slot0 = self.num_state_slots
+        # called with (index of the layer run, stream) after every run when set: for inspection only,
+        # and only meaningful for arrangements that leave nothing pending
+        self.probe: Optional[Callable[[int, torch.Tensor], None]] = None
         self.vectors: Dict[str, torch.Tensor] = {}
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
@@ -54,6 +63,8 @@ class DecoderModel:
         specs = [TensorSpec(self.plan.embedding_name, (V, H))]
         for b in self.blocks:
             specs += b.tensor_specs()
+        for e in self.embedding_extras:
+            specs += e.tensor_specs()
         specs += self.final_norm.tensor_specs()
         for name, rows in self.plan.stream_vectors:
             specs.append(TensorSpec(name, (rows, H), role="vector"))
@@ -65,6 +76,8 @@ class DecoderModel:
         self.embedding = fetch(self.plan.embedding_name)
         for b in self.blocks:
             b.load(fetch)
+        for e in self.embedding_extras:
+            e.load(fetch)
         self.final_norm.load(fetch)
         self.vectors = {name: fetch(name) for name, _ in self.plan.stream_vectors}
         self.head = self.embedding if self.plan.tie_word_embeddings else fetch(self.plan.head_name)
@@ -89,11 +102,13 @@ class DecoderModel:
         return self._slot_specs(self.num_cache_slots, lambda c: c.cache, lambda b: b.cache_spec(), "cache")
 
     def state_specs(self) -> List[Optional[StateSpec]]:
-        return self._slot_specs(self.num_state_slots, lambda c: c.state_slot(), lambda b: b.state_spec(), "state")
+        specs = self._slot_specs(self.num_state_slots, lambda c: c.state_slot(), lambda b: b.state_spec(), "state")
+        return specs + [e.state_spec() for e in self.embedding_extras]
 
     @property
     def graph_safe(self) -> bool:
-        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        return (all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+                and all(e.graph_safe for e in self.embedding_extras))
 
     def check_limits(self, dtype: torch.dtype, max_context: int, page_size: int) -> None:
         for b in self.blocks:
@@ -102,6 +117,7 @@ class DecoderModel:
 
     def weight_bytes(self) -> int:
         n = sum(b.weight_bytes() for b in self.blocks) + self.final_norm.weight_bytes()
+        n += sum(e.weight_bytes() for e in self.embedding_extras)
         n += sum(v.numel() * 4 for v in self.vectors.values())
         return n + self.head.numel() * self.head.element_size()
 
@@ -112,17 +128,21 @@ class DecoderModel:
         """Run every row of the step; return float32 logits [R, vocab] for ctx.logit_rows."""
         h = torch.empty((ctx.T, self.hidden_size), dtype=torch.float32, device=ctx.device)
         kernels.embed_rows(self.embedding, ctx.token_ids, h)
+        for i, e in enumerate(self.embedding_extras):
+            e.add(h, ctx, state_of(self.extra_state_slot0 + i))
         pending = None
-        for call in self.order:
+        for run, call in enumerate(self.order):
             if call.add_vector is not None:
                 # (the pending contribution has not been added yet; the sums commute)
                 kernels.add_row_vector(h, self.vectors[call.add_vector[0]][call.add_vector[1]])
             pending = self.blocks[call.layer].forward(
                 h, pending, ctx, cache_view(call.cache, call.append), state_of(call.state_slot()))
+            if self.probe is not None:
+                self.probe(run, h)
         R = ctx.logit_rows.numel()
         if R == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=ctx.device)
-        if not self.final_norm.takes_unsummed:
+        if not self.final_norm.takes_unsummed or not isinstance(pending, (torch.Tensor, RoutedSum, type(None))):
             pending = summed(pending)
         x = self.final_norm.add_norm_rows(h, pending, ctx.logit_rows, ctx.dtype)
         logits = kernels.linear(x, self.head, out_dtype=torch.float32)

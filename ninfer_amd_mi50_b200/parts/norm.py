@@ -23,15 +23,29 @@ class RmsNorm(Norm):
     graph_safe = True
     takes_unsummed = True
 
-    def __init__(self, size: int, eps: float, prefix: str):
+    def __init__(self, size: int, eps: float, prefix: str, weight_name: str = "weight", one_plus: bool = False):
+        """`one_plus`: the stored weight lies around zero and 1 + w multiplies.  `weight_name` "":
+        the checkpoint names the weight by the norm's own name, without a suffix."""
         self.size, self.eps, self.prefix = int(size), float(eps), prefix
+        self.weight_name, self.one_plus = weight_name, bool(one_plus)
         self.weight: Optional[torch.Tensor] = None
 
+    def _name(self) -> str:
+        return self.prefix + self.weight_name if self.weight_name else self.prefix.rstrip(".")
+
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.prefix + "weight", (self.size,), role="vector", init="norm")]
+        return [TensorSpec(self._name(), (self.size,), role="vector", init="linear" if self.one_plus else "norm")]
 
     def load(self, fetch: Fetch) -> None:
-        self.weight = fetch(self.prefix + "weight")
+        self.weight = fetch(self._name())
+        if self.one_plus:
+            # held as 1 + w: the float32 sum is the one a kernel would form from w anyway
+            self.weight = (self.weight + 1.0).contiguous()
+
+    def add_scaled_norm(self, h, delta, scale, out_dtype, bias=None):
+        """h += scale * norm(delta + bias) (in place, 32-bit): the norm sits on a sublayer's output,
+        not on its input.  Returns the updated stream in `out_dtype` (None: nothing)."""
+        return kernels.scaled_norm_add(h, delta, bias, self.weight, scale, self.eps, out_dtype)
 
     def weight_bytes(self) -> int:
         return self.size * 4

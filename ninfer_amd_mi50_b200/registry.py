@@ -17,7 +17,7 @@ from typing import Any, Callable, Dict
 
 from .config.model_config import ConfigError, ModelPlan, PartSpec
 
-PART_CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+PART_CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding")
 
 
 @dataclass(frozen=True)
