@@ -69,11 +69,15 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_row_stride,
                         (size_t)(j % page_size) * D;
         vrow = krow + (size_t)Hkv * head_stride;
         float dot = 0.f;
-        for (int d = 0; d < D; d += 8) {
-          float kk[8];
-          load8(krow + d, kk);
+        if (D % 8 == 0) {
+          for (int d = 0; d < D; d += 8) {
+            float kk[8];
+            load8(krow + d, kk);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(q[d + e], kk[e], dot);
+            for (int e = 0; e < 8; ++e) dot = fmaf(q[d + e], kk[e], dot);
+          }
+        } else {                             // a head size whose rows are not 16-byte aligned
+          for (int d = 0; d < D; ++d) dot = fmaf(q[d], to_float(krow[d]), dot);
         }
         s = dot * scale - slope * (float)(pos - j);
       }
@@ -123,7 +127,7 @@ extern "C" int nf_paged_attention_generic(const void* qkv, int q_row_stride, con
                                           cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: bad sizes T=%d Hq=%d Hkv=%d", T, Hq, Hkv);
-  NF_REQUIRE(D % 16 == 0 && D >= 16 && D <= 256, "attention: head_dim %d must be a multiple of 16 in [16, 256]", D);
+  NF_REQUIRE(D >= 1 && D <= 256, "attention: head_dim %d must lie in [1, 256]", D);
   dim3 grid(T, (Hq + 3) / 4);
   const size_t smem = 4 * D * sizeof(float);
   if (dtype == kF32)

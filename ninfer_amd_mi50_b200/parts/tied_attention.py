@@ -42,7 +42,8 @@ class TiedValueAttention(Mixer):
                  qk_bias: bool = True, head_gate: bool = True, tensor_names=None):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads do not divide into {kv_heads} groups")
-        kernels.check_head_dim(head_dim)
+        if not 1 <= int(head_dim) <= 256:
+            raise ValueError(f"head_dim={head_dim} outside 1..256")
         self.hidden_size, self.heads, self.kv_heads, self.head_dim = int(hidden_size), int(heads), int(kv_heads), int(head_dim)
         self.scale, self.eps, self.prefix = float(scale), float(eps), prefix
         self.window = int(window) if window else None

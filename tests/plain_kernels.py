@@ -165,15 +165,24 @@ def route(x, w_router, E, k, norm_topk, split=None):
     return idx, wts, ext, moe_plan(idx, E)
 
 
-def moe_experts(x, w13, w2, plan, k, gathered=None):
-    return moe_gemm2(moe_gemm1(x, w13, plan, k), w2, plan)
+def _gated(g, u, act):
+    """silu(g) * u, or for act = (2, limit, alpha) the capped form."""
+    if act is not None and act[0] == 2:
+        g = torch.clamp(g, max=act[1])
+        u = torch.clamp(u, min=-act[1], max=act[1])
+        return g / (1 + torch.exp(-act[2] * g)) * (u + 1)
+    return g / (1 + torch.exp(-g)) * u
 
 
-def moe_gemm1(x, w13, plan, k, gathered=None):
+def moe_experts(x, w13, w2, plan, k, gathered=None, act=None):
+    return moe_gemm2(moe_gemm1(x, w13, plan, k, act=act), w2, plan)
+
+
+def moe_gemm1(x, w13, plan, k, gathered=None, act=None):
     T, H = x.shape
     E, two_i, _ = w13.shape
     inner = two_i // 2
-    act = torch.zeros((T * k, inner), dtype=torch.float32, device=x.device)
+    out = torch.zeros((T * k, inner), dtype=torch.float32, device=x.device)
     off = plan.offsets.cpu().tolist()
     order = plan.order.cpu().tolist()
     for e in range(E):
@@ -181,8 +190,8 @@ def moe_gemm1(x, w13, plan, k, gathered=None):
             xr = _f(x[order[p] // k])
             gu = _f(w13[e]) @ xr
             g, u = gu[:inner], gu[inner:]
-            act[p] = g / (1 + torch.exp(-g)) * u
-    return act.to(x.dtype)
+            out[p] = _gated(g, u, act)
+    return out.to(x.dtype)
 
 
 def moe_gemm2(act, w2, plan, plan_is_older=False):
