@@ -17,9 +17,21 @@ from typing import Dict, List, Optional
 import torch
 
 
+# (generator, relative size) or None: every projection's output is then disturbed by that much, as a
+# rounding to few bits would.  The tests use it to find the rows whose logits hang on a rounding
+# (a sum that nearly cancels in front of a norm that blows it up again): no arithmetic of 8 bits
+# can be held to a per cent there.
+NOISE = None
+
+
 def lin(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
     y = x @ w.T
-    return y if b is None else y + b
+    if b is not None:
+        y = y + b
+    if NOISE is not None:
+        gen, size = NOISE
+        y = y * (1.0 + size * torch.randn(y.shape, generator=gen, dtype=y.dtype))
+    return y
 
 
 def silu(x: torch.Tensor) -> torch.Tensor:

@@ -69,23 +69,43 @@ def run(runner, steps, routing=True):
     return ({k: torch.cat(v) for k, v in got.items()}, {k: [torch.cat(v) for v in per] for k, per in chosen.items()} if routing else {})
 
 
-def compare(got, want, dtype, what, bf16_bound=8e-2):
+def compare(got, want, dtype, what, bf16_bound=8e-2, touchy=None):
     """float32 is the sharp comparison: 1e-4 of the largest logit for every row.  bfloat16 rounds
     every activation between kernels to 8 bits: every row within 8 %, the median row (of a request
-    of 16 rows or more) within 1.5 %.  The design norms every sublayer's OUTPUT row by row, so a row
-    whose mixer output nearly cancels is blown up to unit size, its rounding with it: one row in
-    fifty may therefore lie beyond 8 % (but within 25 %) in bfloat16."""
+    of 16 rows or more) within 1.5 %.  `touchy` marks rows whose logits hang on a rounding (see
+    `touchy_rows`); in bfloat16 they are only asked to be finite, and may be one row in ten."""
     scale = want.abs().max().item()
     err = (got - want).abs().max(dim=1).values / scale
     if dtype == "float32":
         assert err.max().item() <= 1e-4, f"{what}: row {int(err.argmax())} of {len(err)} differs by {err.max().item():.3e} of the scale"
         return err.max().item()
-    over = int((err > bf16_bound).sum())
-    assert over <= len(err) // 50 + (1 if len(err) >= 25 else 0) and err.max().item() <= 0.25, \
-        f"{what}: {over} rows of {len(err)} beyond {bf16_bound}, the worst (row {int(err.argmax())}) by {err.max().item():.3e} of the scale"
+    assert torch.isfinite(got).all(), what
+    if touchy is not None and touchy.any():
+        assert int(touchy.sum()) <= len(err) // 10 + 1, f"{what}: {int(touchy.sum())} of {len(err)} rows hang on a rounding"
+        err = err[~touchy]
+        if len(err) == 0:
+            return 0.0
+    assert err.max().item() <= bf16_bound, f"{what}: row {int(err.argmax())} of {len(err)} differs by {err.max().item():.3e} of the scale"
     if len(err) >= 16:
         assert err.median().item() <= 1.5e-2, f"{what}: the median row differs by {err.median().item():.3e} of the scale"
     return err.max().item()
+
+
+def touchy_rows(cfg, w, tokens, chosen, want, tries=3):
+    """Rows whose logits move by more than 2 % of the scale when every projection's output is
+    disturbed by 2^-9 of its size, in any of a few tries.  The design norms every sublayer's OUTPUT
+    row by row: where a mixer's output nearly cancels (a request's first token, whose linear
+    attention output is sign(q . k) v), the norm blows the rounding up with it."""
+    scale = want.abs().max().item()
+    out = torch.zeros(want.shape[0], dtype=torch.bool)
+    try:
+        for i in range(tries):
+            PD.NOISE = (torch.Generator().manual_seed(50 + i), 2.0 ** -9)
+            noisy = PD.forward(tokens, w, cfg, chosen=chosen)
+            out |= (noisy - want).abs().max(dim=1).values / scale > 2e-2
+    finally:
+        PD.NOISE = None
+    return out
 
 
 def expected(cfg, w, tokens, dtype, chosen):
@@ -118,7 +138,9 @@ def test_every_way_of_cutting_matches_the_plain_model(folder, dtype, how):
     got, chosen = run(runner, make(reqs))
     assert all(n == pool // 16 for n in runner.cache.pages_free())
     for r, toks in reqs.items():
-        compare(got[r], expected(cfg, w, toks, dtype, chosen[r]), dtype, f"{name} {how} {r}")
+        want = expected(cfg, w, toks, dtype, chosen[r])
+        touchy = touchy_rows(cfg, w, toks, chosen[r], want) if dtype == "bfloat16" else None
+        compare(got[r], want, dtype, f"{name} {how} {r}", touchy=touchy)
 
 
 # ---- each mechanism alone ---------------------------------------------------------------------
@@ -301,7 +323,9 @@ def test_long_decoding_lets_the_window_pass_over_decoded_tokens(folder, dtype):
     toks = random_tokens(236, cfg["vocab"], 77)
     runner = load_runner(d, options=options(dtype))
     got, chosen = run(runner, schedules.tail_decoded({"a": toks}, tail=229))
-    compare(got["a"], expected(cfg, w, toks, dtype, chosen["a"]), dtype, f"{name} long decoding")
+    want = expected(cfg, w, toks, dtype, chosen["a"])
+    touchy = touchy_rows(cfg, w, toks, chosen["a"], want) if dtype == "bfloat16" else None
+    compare(got["a"], want, dtype, f"{name} long decoding", touchy=touchy)
     assert all(n == 1024 // 16 for n in runner.cache.pages_free())
 
 
