@@ -13,6 +13,10 @@
 // exponential is ``ex2.approx`` on scores pre-multiplied by log2 e: 2^-22 relative, far below
 // the bfloat16 rounding of P that follows).
 // Key j is visible to a row at position p iff max(0, p - window + 1) <= j <= p.
+// Options: `keep_first` keeps a request's first keys visible when the window has passed them (the
+// aligned blocks that hold them are walked first, then the window's); `slopes` takes
+// slope_h * (p - j) off head h's score of key j; `gate` multiplies head h's output by
+// sigmoid(gate[row, h]).
 // Key blocks are aligned to multiples of 64 keys, so the order of a row's sums depends on
 // its own position only, not on how the prompt was cut.
 #include "common.cuh"
@@ -55,7 +59,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
                          const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table,
                          int bt_width, const int* __restrict__ positions, const int* __restrict__ seg_row0,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
-                         int page_size, int num_pages, int window, float scale) {
+                         int page_size, int num_pages, int window, float scale,
+                         const float* __restrict__ slopes, int keep_first, const float* __restrict__ gate,
+                         int gate_ld) {
   constexpr int DS = D + 8;             // padded row stride in elements
   constexpr int LPR = D / 8;            // 16-byte pieces per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -77,7 +83,11 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   int lo_tile = 0;
   if (window > 0 && pos_first - window + 1 > 0) lo_tile = pos_first - window + 1;
   const int kb_first = (lo_tile / kBKeys) * kBKeys;
-  const int n_blocks = (pos_last - kb_first) / kBKeys + 1;
+  // blocks of kept first keys that lie wholly before the window's first block, then the window's
+  const int n_kept = (min(keep_first, kb_first) + kBKeys - 1) / kBKeys;
+  const int n_blocks = n_kept + (pos_last - kb_first) / kBKeys + 1;
+  const float slope2 = slopes ? slopes[h] * kLog2e : 0.f;
+  auto block_start = [&](int blk) { return blk < n_kept ? blk * kBKeys : kb_first + (blk - n_kept) * kBKeys; };
 
   // ---- Q tile ------------------------------------------------------------------------------
   for (int c = threadIdx.x; c < kBQ * LPR; c += blockDim.x) {
@@ -91,7 +101,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   auto load_block = [&](int blk, int stage) {
     __nv_bfloat16* Ks = KVs + (size_t)stage * 2 * kBKeys * DS;
     __nv_bfloat16* Vs = Ks + kBKeys * DS;
-    const int kb = kb_first + blk * kBKeys;
+    const int kb = block_start(blk);
     for (int c = threadIdx.x; c < kBKeys * LPR; c += blockDim.x) {
       const int r = c / LPR, piece = c - r * LPR;
       const int j = kb + r;
@@ -132,7 +142,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
     __syncthreads();
     const __nv_bfloat16* Ks = KVs + (size_t)(blk & 1) * 2 * kBKeys * DS;
     const __nv_bfloat16* Vs = Ks + kBKeys * DS;
-    const int kb = kb_first + blk * kBKeys;
+    const int kb = block_start(blk);
 
     // a warp whose 16 rows lie beyond the tile's rows, or wholly before this block's keys,
     // only helps with the copies
@@ -163,7 +173,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
     // every key of the block visible to every row of the warp: no mask to apply
     const bool all_visible = warp * 16 + 15 < n_rows && kb + kBKeys - 1 <= pos_first + warp * 16 &&
                              (window <= 0 || kb >= pos_first + warp * 16 + 15 - window + 1);
-    if (all_visible) {
+    if (all_visible && slope2 == 0.f) {
 #pragma unroll
       for (int n = 0; n < kBKeys / 8; ++n)
 #pragma unroll
@@ -181,7 +191,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
           const int p = hi_row ? p_hi : p_lo;
           const int w = hi_row ? w_hi : w_lo;
           const bool row_ok = (hi_row ? r_hi : r_lo) < n_rows;
-          const float v = (row_ok && j <= p && j >= w) ? s[n][i] * sc2 : -INFINITY;
+          const float v = (row_ok && j <= p && (j >= w || j < keep_first))
+                              ? fmaf(-slope2, (float)(p - j), s[n][i] * sc2) : -INFINITY;
           s[n][i] = v;
           mx[i >> 1] = fmaxf(mx[i >> 1], v);
         }
@@ -241,7 +252,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   for (int r = 0; r < 2; ++r) {
     const int row = r ? r_hi : r_lo;
     if (row >= n_rows) continue;
-    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    if (gate) inv *= 1.f / (1.f + expf(-gate[(size_t)(row0 + row) * gate_ld + h]));
     __nv_bfloat16* dst = out + (size_t)(row0 + row) * Hq * D + (size_t)h * D;
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) {
@@ -257,7 +269,8 @@ template <int D>
 static int launch_prefill(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                           int bt_width, const int* positions, const int* seg_row0, const int* tiles,
                           int n_tiles, void* out, int Hq, int Hkv, int page_size, int num_pages, int window,
-                          float scale, cudaStream_t stream) {
+                          float scale, const float* slopes, int keep_first, const float* gate, int gate_ld,
+                          cudaStream_t stream) {
   const size_t smem = (size_t)(kBQ + 4 * kBKeys) * (D + 8) * sizeof(__nv_bfloat16);
   static bool set = false;
   if (smem > 48 * 1024 && !set) {
@@ -267,7 +280,8 @@ static int launch_prefill(const void* qkv, int q_row_stride, const void* pages, 
   dim3 grid(n_tiles, Hq);
   prefill_attention_kernel<D><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions,
-      seg_row0, tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size, num_pages, window, scale);
+      seg_row0, tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size, num_pages, window, scale, slopes, keep_first, gate,
+      gate_ld);
   return check_launch("prefill_attention");
 }
 
@@ -279,16 +293,20 @@ extern "C" int nf_prefill_attention_tile_rows() { return kBQ; }
 
 // bfloat16; head_dim a multiple of 16 up to 128.  `tiles` is int32 [n_ctas, 2, 2]: for every CTA two
 // tiles as (segment, first row), each at most 64 consecutive rows of one segment; the second may
-// be (-1, -1).
-extern "C" int nf_prefill_attention(const void* qkv, int q_row_stride, const void* pages,
-                                    const int* block_table, int bt_width, const int* positions,
-                                    const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,
-                                    int Hkv, int D, int page_size, int num_pages, int window, float scale,
-                                    cudaStream_t stream) {
+// be (-1, -1).  slopes float32 [Hq] or null; keep_first >= 0 (it counts only with a window); gate
+// float32 [T, gate_ld] (column h: head h's gate logit) or null.
+extern "C" int nf_prefill_attention_biased(const void* qkv, int q_row_stride, const void* pages,
+                                           const int* block_table, int bt_width, const int* positions,
+                                           const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,
+                                           int Hkv, int D, int page_size, int num_pages, int window, float scale,
+                                           const float* slopes, int keep_first, const float* gate, int gate_ld,
+                                           cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   NF_REQUIRE(n_tiles > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535, "prefill attention: bad sizes tiles=%d Hq=%d Hkv=%d", n_tiles, Hq, Hkv);
   NF_REQUIRE(q_row_stride % 8 == 0 && (uintptr_t)qkv % 16 == 0, "prefill attention: query rows must be 16-byte aligned");
-#define NF_PF(DD) case DD: return launch_prefill<DD>(qkv, q_row_stride, pages, block_table, bt_width, positions, seg_row0, tiles, n_tiles, out, Hq, Hkv, page_size, num_pages, window, scale, stream);
+  NF_REQUIRE(keep_first >= 0 && (!gate || gate_ld >= Hq), "prefill attention: bad options");
+  if (window <= 0) keep_first = 0;
+#define NF_PF(DD) case DD: return launch_prefill<DD>(qkv, q_row_stride, pages, block_table, bt_width, positions, seg_row0, tiles, n_tiles, out, Hq, Hkv, page_size, num_pages, window, scale, slopes, keep_first, gate, gate_ld, stream);
   switch (D) {
     NF_PF(16) NF_PF(32) NF_PF(48) NF_PF(64) NF_PF(80) NF_PF(96) NF_PF(112) NF_PF(128)
     default:
@@ -296,4 +314,14 @@ extern "C" int nf_prefill_attention(const void* qkv, int q_row_stride, const voi
       return 1;
   }
 #undef NF_PF
+}
+
+extern "C" int nf_prefill_attention(const void* qkv, int q_row_stride, const void* pages,
+                                    const int* block_table, int bt_width, const int* positions,
+                                    const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,
+                                    int Hkv, int D, int page_size, int num_pages, int window, float scale,
+                                    cudaStream_t stream) {
+  return nf_prefill_attention_biased(qkv, q_row_stride, pages, block_table, bt_width, positions, seg_row0, tiles,
+                                     n_tiles, out, Hq, Hkv, D, page_size, num_pages, window, scale, nullptr, 0, nullptr,
+                                     0, stream);
 }

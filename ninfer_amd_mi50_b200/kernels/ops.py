@@ -587,11 +587,26 @@ def biased_window_attention(q: torch.Tensor, Hq: int, Hkv: int, D: int, pages: t
     if T == 0:
         return out
     gate_p = c_void_p(gate.data_ptr() + 4 * gate_col0) if gate is not None else None
+    gate_ld = gate.shape[1] if gate is not None else 0
+    keep = keep_first if window > 0 else 0
+    if (q.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic" and D in PREFILL_HEAD_DIMS
+            and q.shape[1] % 8 == 0 and pages.is_contiguous()):
+        # the flash kernel on tensor cores: tiles of 64 rows of a segment, key blocks of 64
+        tiles = None
+        if getattr(ctx, "all_single", False) and getattr(ctx, "seg_len_host", None) is not None:
+            tiles, n_tiles = ctx.one_row_tiles()
+        elif getattr(ctx, "seg_len_host", None) is not None and getattr(ctx, "seg_pos0_host", None) is not None:
+            tiles, n_tiles = _tiles(ctx, PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK, True, 1)
+        if tiles is not None:
+            _lib.call("nf_prefill_attention_biased", _p(q), c_int(q.shape[1]), _p(pages), _p(block_table),
+                      c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles), c_int(n_tiles),
+                      _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size), c_int(pages.shape[0]), c_int(window),
+                      c_float(scale), _p(slopes), c_int(keep), gate_p, c_int(gate_ld), _stream())
+            return out
     _lib.call("nf_paged_attention_generic", _p(q), c_int(q.shape[1]), _p(pages), _p(block_table),
               c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out), c_int(T), c_int(Hq),
               c_int(Hkv), c_int(D), c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale),
-              c_int(_dt(q)), _p(slopes), c_int(keep_first if window > 0 else 0), gate_p,
-              c_int(gate.shape[1] if gate is not None else 0), _stream())
+              c_int(_dt(q)), _p(slopes), c_int(keep), gate_p, c_int(gate_ld), _stream())
     return out
 
 

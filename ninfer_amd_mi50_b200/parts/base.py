@@ -184,6 +184,16 @@ class StepContext:
         self._tiles[key] = (t, n_tiles)
         return t, n_tiles
 
+    def one_row_tiles(self) -> Tuple[torch.Tensor, int]:
+        """For a step whose every segment brings one row: a tile a segment, as the flash kernels take
+        them (int32 [S, 2, 2] of (segment, first row), the second entry (-1, -1)).  It depends on the
+        number of segments alone, so a step that is captured into a graph may use it: the tensor is
+        made on the first (uncaptured) run and kept."""
+        if "one_row" not in self._tiles:
+            flat = [v for s in range(self.S) for v in (s, s, -1, -1)]
+            self._tiles["one_row"] = (torch.tensor(flat, dtype=torch.int32).reshape(self.S, 2, 2).to(self.device), self.S)
+        return self._tiles["one_row"]
+
     def single_rows(self) -> Tuple[Optional[torch.Tensor], int]:
         """Rows of the segments that bring exactly one row (decoded tokens, or a prompt's last
         token arriving alone), as (int32 tensor on the device, count); (None, 0) if there are

@@ -265,17 +265,21 @@ def plain_attention_rows(q, keys, vals, pos, scale, slopes, window, keep_first):
     return out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,keep_first", [(40, 6), (16, 16), (17, 0), (64, 1)])
-def test_one_loud_key_is_heard_just_inside_and_not_just_outside_every_edge(dtype, window, keep_first):
+@pytest.mark.parametrize("dtype,D,general", [(torch.float32, 16, True), (torch.bfloat16, 16, False), (torch.bfloat16, 64, False),
+                                             (torch.bfloat16, 16, True), (torch.bfloat16, 24, True)])
+@pytest.mark.parametrize("window,keep_first", [(40, 6), (16, 16), (17, 0), (64, 1), (3, 70)])
+def test_one_loud_key_is_heard_just_inside_and_not_just_outside_every_edge(monkeypatch, dtype, D, general, window, keep_first):
     """The cache is filled by hand: every key is faint but one, whose score towers.  Placed just
     inside the window, on a page's border, among the kept first tokens or far back, it must take the
     whole output; placed just outside the window or just after the kept tokens it must not show.
-    Rows are served both as a prompt's portion and as single decoded tokens."""
+    Rows are served both as a prompt's portion and as single decoded tokens, by the flash kernel
+    (bfloat16, head sizes that are multiples of 16) and by the general one."""
     from ninfer_amd_mi50_b200 import kernels
     from ninfer_amd_mi50_b200.parts.base import StepContext
     dev = torch.device("cuda")
-    H, G, D, page, n = 4, 2, 16, 16, 150
+    if general and dtype == torch.bfloat16:
+        monkeypatch.setitem(kernels.TUNING, "bf16_attention", "generic")      # the general kernel, not the flash one
+    H, G, page, n = 4, 2, 16, 150
     gen = torch.Generator().manual_seed(3)
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32)
     pos = n - 1
