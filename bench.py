@@ -6,6 +6,7 @@
     python bench.py --long-prefill         # adds prefill of 8,192 and 32,768 tokens in portions of 2,048 (--portion)
     python bench.py --config check-fp32    # the whole model in 32-bit at A2.7B sizes against the plain model
     python bench.py --config vekasun       # the Vekasun design beside Qwen2-MoE at equal layer sizes (--sizes), kernel by kernel
+    python bench.py --config difavik       # the same for the Difavik design
 
 One JSON line on stdout.  A "step" is one decode step of a batch of 8 requests, each
 holding a context of about 2,048 tokens (the context length of the named configuration's
@@ -192,15 +193,16 @@ def check_fp32(args) -> int:
 
 
 def compare_designs(args, W, K) -> int:
-    """Prefill and decode throughput of the Vekasun design beside Qwen2-MoE at equal layer sizes
-    (four layers, random weights), and each kernel of a prompt step and of a decode step against
-    its roofline.  One JSON line."""
+    """Prefill and decode throughput of the Vekasun or the Difavik design beside Qwen2-MoE at equal
+    layer sizes (four layers, random weights), and each kernel of a prompt step and of a decode
+    step against its roofline.  One JSON line."""
     from ninfer_amd_mi50_b200.kernels import compare
     pk = peaks()
     clocks = ClockSampler()
     clocks.start()
-    sizes = compare.run_comparison([s for s in args.sizes.split(",") if s], pk, steps=min(K, 32), warmup=W)
-    print(json.dumps({"comparison": "Vekasun beside Qwen2-MoE at equal layer sizes", "dtype": "bf16", "layers": compare.LAYERS,
+    sizes = compare.run_comparison([s for s in args.sizes.split(",") if s], pk, steps=min(K, 32), warmup=W,
+                                   design=args.config)
+    print(json.dumps({"comparison": f"{args.config.capitalize()} beside Qwen2-MoE at equal layer sizes", "dtype": "bf16", "layers": compare.LAYERS,
                       "data": "synthetic (random weights, random token ids, random cache)", "peaks": pk,
                       "sizes": sizes, "clocks": clocks.stop()}))
     return 0
@@ -212,8 +214,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="a2.7b", choices=sorted(PROFILES) + ["check-fp32", "vekasun"])
-    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="vekasun: named layer sizes, with commas between them")
+    ap.add_argument("--config", default="a2.7b", choices=sorted(PROFILES) + ["check-fp32", "vekasun", "difavik"])
+    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="vekasun, difavik: named layer sizes, with commas between them")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers, for a quick look")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--long-prefill", action="store_true", help="also time prompts of 8,192 and 32,768 tokens")
@@ -236,7 +238,7 @@ def main() -> int:
     K = max(1, args.steps)
     if args.config == "check-fp32":
         return check_fp32(args)
-    if args.config == "vekasun":
+    if args.config in ("vekasun", "difavik"):
         return compare_designs(args, W, K)
     CONFIG, FULL_LAYERS, model_name, PROMPT, value_batch, point_batches = PROFILES[args.config]
     args.layers = args.layers or FULL_LAYERS

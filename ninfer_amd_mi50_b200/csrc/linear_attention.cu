@@ -9,135 +9,247 @@
 // q and k head (pair (i, i + rot/2) by the angle pos * f_i), and k a scale.  Everything after
 // the projection is float32: angles, the rotated and scaled vectors, the state, the sums.
 //
-// One CTA serves 16 value columns of one (request, head) and walks the request's rows of the step
-// in order.  A column's D state entries lie in the registers of 8 lanes (entry i with lane i % 8);
-// the step's q, k, v are staged 16 tokens at a time in shared memory (activation, rotation and
-// scale applied while staging), so the token loop itself has no block-wide barrier.  The sum
-// over a column is three shuffles.  A token's result depends on earlier tokens only through S,
-// which holds the same bits however the request was cut into steps.
+// One CTA of 128 threads serves 128 / LANES value columns of one (request, head) and walks the
+// request's rows of the step in order.  A column's D state entries lie in the registers of LANES
+// lanes (8, or 16 for heads wider than 64), EPL consecutive entries a lane.  The step's q, k, v
+// are staged CH tokens at a time in shared memory (activation, rotation and scale applied while
+// staging), so the token loop itself has no block-wide barrier; the next chunk's raw values are
+// asked for before the current chunk's token loop and wait in registers, so that their way from
+// memory lies under the arithmetic.  A lane reads its entries of k and q as 16-byte pieces (rows
+// padded by 4 floats every EPL, which keeps the lanes of a column on different banks); the sum
+// over a column is log2(LANES) shuffles.  A token's result depends on earlier tokens only
+// through S, which holds the same bits however the request was cut.
 //
 // The state of a slot is laid out [head][value column][D]: a column's entries are contiguous, so
-// the 8 lanes of a column read and write whole 32-byte sectors.
+// the lanes of a column read and write whole 32-byte sectors.
 #define NF_CHAIN_CLASS 2
 #include "common.cuh"
 
 namespace nf {
 
-constexpr int kLaLanes = 8;       // lanes that share a value column
-constexpr int kLaCols = 16;       // value columns a CTA
-constexpr int kLaChunk = 16;      // tokens staged at a time
+constexpr int kLaThreads = 128;
 
-template <typename T, int EPL>    // EPL: state entries a lane, D <= 8 * EPL
-__global__ void __launch_bounds__(kLaLanes* kLaCols)
-decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0, int v_col0,
-                              const float* __restrict__ decay, const float* __restrict__ inv_freq, int rot,
-                              float k_scale, int use_silu, float* __restrict__ state, long slot_stride,
-                              const int* __restrict__ seg_row0, const int* __restrict__ seg_slot,
-                              const int* __restrict__ seg_pos0, float* __restrict__ out, int H, int D, int V) {
-  constexpr int DP = kLaLanes * EPL;                       // padded D
-  __shared__ float sq[kLaChunk][DP];
-  __shared__ float sk[kLaChunk][DP];
-  __shared__ float sv[kLaChunk][kLaCols];
-  const int seg = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kLaCols;
-  const int tid = threadIdx.x, lane = tid % kLaLanes, col = col0 + tid / kLaLanes;
-  const bool live = col < V;
-  chain_release_if_small();
-  chain_wait(src, state);
-  const int row0 = seg_row0[seg], rows = seg_row0[seg + 1] - row0;
-  const int pos0 = seg_pos0[seg];
-  const float g = decay[head];
-  float* sp = state + (size_t)seg_slot[seg] * slot_stride + ((size_t)head * V + (live ? col : 0)) * D;
-  float s[EPL];
-#pragma unroll
-  for (int e = 0; e < EPL; ++e) {
-    const int i = lane + kLaLanes * e;
-    s[e] = (live && i < D) ? sp[i] : 0.f;
-  }
-  const int half = rot / 2;
-  for (int c0 = 0; c0 < rows; c0 += kLaChunk) {
-    const int n = min(kLaChunk, rows - c0);
-    __syncthreads();                                       // the previous chunk has been read
-    // stage q and k: thread per (token, dimension); a rotated pair is handled by its lower index
-    for (int x = tid; x < n * DP; x += blockDim.x) {
-      const int t = x / DP, i = x - t * DP;
-      if (i >= D) { sq[t][i] = 0.f; sk[t][i] = 0.f; continue; }
-      if (i >= half && i < rot) continue;                  // written with its partner
-      const T* r = src + (size_t)(row0 + c0 + t) * ld + (size_t)head * D;
-      float q0 = to_float(r[q_col0 + i]), k0 = to_float(r[k_col0 + i]);
-      if (use_silu) { q0 = q0 / (1.f + expf(-q0)); k0 = k0 / (1.f + expf(-k0)); }
-      if (i < half) {
-        float q1 = to_float(r[q_col0 + i + half]), k1 = to_float(r[k_col0 + i + half]);
-        if (use_silu) { q1 = q1 / (1.f + expf(-q1)); k1 = k1 / (1.f + expf(-k1)); }
-        const float angle = (float)(pos0 + c0 + t) * inv_freq[i];
-        const float cs = cosf(angle), sn = sinf(angle);
-        sq[t][i] = q0 * cs - q1 * sn;
-        sq[t][i + half] = q1 * cs + q0 * sn;
-        sk[t][i] = (k0 * cs - k1 * sn) * k_scale;
-        sk[t][i + half] = (k1 * cs + k0 * sn) * k_scale;
-      } else {
-        sq[t][i] = q0;
-        sk[t][i] = k0 * k_scale;
-      }
-    }
-    for (int x = tid; x < n * kLaCols; x += blockDim.x) {
-      const int t = x / kLaCols, j = x - t * kLaCols;
-      float v = 0.f;
-      if (col0 + j < V) {
-        v = to_float(src[(size_t)(row0 + c0 + t) * ld + v_col0 + (size_t)head * V + col0 + j]);
-        if (use_silu) v = v / (1.f + expf(-v));
-      }
-      sv[t][j] = v;
-    }
-    __syncthreads();
-    for (int t = 0; t < n; ++t) {
-      const float v = sv[t][tid / kLaLanes];
-      float o = 0.f;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const int i = lane + kLaLanes * e;
-        s[e] = fmaf(g, s[e], sk[t][i] * v);
-        o = fmaf(s[e], sq[t][i], o);
-      }
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      if (live && lane == 0) out[(size_t)(row0 + c0 + t) * H * V + (size_t)head * V + col] = o;
-    }
-  }
-  if (live) {
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const int i = lane + kLaLanes * e;
-      if (i < D) sp[i] = s[e];
+__device__ __forceinline__ float la_act(float x, int use_silu) { return use_silu ? x / (1.f + expf(-x)) : x; }
+// One rotated pair of q and of k (already through `la_act`), by the angle pos * f, k scaled after
+// the turn.  The products are written out so that both kernels below round alike.
+__device__ __forceinline__ void la_turn(float q0, float q1, float k0, float k1, float angle, float k_scale, float& oq0,
+                                        float& oq1, float& ok0, float& ok1) {
+  const float cs = cosf(angle), sn = sinf(angle);
+  oq0 = __fsub_rn(__fmul_rn(q0, cs), __fmul_rn(q1, sn));
+  oq1 = __fadd_rn(__fmul_rn(q1, cs), __fmul_rn(q0, sn));
+  ok0 = __fmul_rn(__fsub_rn(__fmul_rn(k0, cs), __fmul_rn(k1, sn)), k_scale);
+  ok1 = __fmul_rn(__fadd_rn(__fmul_rn(k1, cs), __fmul_rn(k0, sn)), k_scale);
+}
+
+// For steps with prompt portions: q and k of every row, activated, turned and scaled ONCE, as
+// float32 [T, q: H x D | k: H x D].  (The recurrence kernel's CTAs each serve a few value columns
+// of a head; left to them, every one of them would repeat this work for the whole head.)
+template <typename T>
+__global__ void linear_attention_prepare_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0,
+                                                const float* __restrict__ inv_freq, int rot, float k_scale, int use_silu,
+                                                const int* __restrict__ positions, float* __restrict__ out, int H, int D) {
+  const int t = blockIdx.x;
+  chain_wait(src);
+  const int half = rot / 2, units = half + (D - rot);
+  const T* row = src + (size_t)t * ld;
+  float* o = out + (size_t)t * 2 * H * D;
+  const float fpos = (float)positions[t];
+  for (int x = blockIdx.y * blockDim.x + threadIdx.x; x < H * units; x += gridDim.y * blockDim.x) {
+    const int head = x / units, u = x - head * units;
+    const int base = head * D;
+    if (u < half) {
+      float a, b, c, d;
+      la_turn(la_act(to_float(row[q_col0 + base + u]), use_silu), la_act(to_float(row[q_col0 + base + u + half]), use_silu),
+              la_act(to_float(row[k_col0 + base + u]), use_silu), la_act(to_float(row[k_col0 + base + u + half]), use_silu),
+              fpos * inv_freq[u], k_scale, a, b, c, d);
+      o[base + u] = a; o[base + u + half] = b;
+      o[H * D + base + u] = c; o[H * D + base + u + half] = d;
+    } else {
+      const int i = rot + (u - half);
+      o[base + i] = la_act(to_float(row[q_col0 + base + i]), use_silu);
+      o[H * D + base + i] = __fmul_rn(la_act(to_float(row[k_col0 + base + i]), use_silu), k_scale);
     }
   }
 }
 
-template <typename T, int EPL>
+template <typename T, int EPL, int LANES, int CH>    // D <= LANES * EPL; CH tokens staged at a time
+__global__ void __launch_bounds__(kLaThreads)
+decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0, int v_col0,
+                              const float* __restrict__ decay, const float* __restrict__ inv_freq, int rot,
+                              float k_scale, int use_silu, float* __restrict__ state, long slot_stride,
+                              const int* __restrict__ seg_row0, const int* __restrict__ seg_slot,
+                              const int* __restrict__ seg_pos0, float* __restrict__ out, int H, int D, int V,
+                              const float* __restrict__ prepared) {
+  constexpr int COLS = kLaThreads / LANES;                 // value columns a CTA
+  constexpr bool VEC = EPL % 4 == 0;
+  constexpr int PAD = VEC ? 4 : 0;
+  constexpr int DPAD = LANES * EPL;                        // D rounded up
+  constexpr int DP = LANES * (EPL + PAD);                  // padded row of q or k in shared memory
+  constexpr int RMAX = (CH * DPAD + kLaThreads - 1) / kLaThreads;    // staging units a thread
+  constexpr int VMAX = (CH * COLS + kLaThreads - 1) / kLaThreads;
+  __shared__ __align__(16) float sq[CH][DP];
+  __shared__ __align__(16) float sk[CH][DP];
+  __shared__ float sv[CH][COLS];
+  const int seg = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
+  const int tid = threadIdx.x, lane = tid % LANES, cidx = tid / LANES, col = col0 + cidx;
+  const bool live = col < V;
+  chain_release_if_small();
+  chain_wait(src, state, prepared);
+  const int row0 = seg_row0[seg], rows = seg_row0[seg + 1] - row0;
+  const int pos0 = seg_pos0[seg];
+  const float g = decay[head];
+  float* sp = state + (size_t)seg_slot[seg] * slot_stride + ((size_t)head * V + (live ? col : 0)) * D + lane * EPL;
+  float s[EPL];
+  const bool vec_state = VEC && D % 4 == 0 && (slot_stride % 4 == 0) && ((uintptr_t)state % 16 == 0);
+  if (vec_state) {
+#pragma unroll
+    for (int e = 0; e < EPL; e += 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live && lane * EPL + e < D) v = *reinterpret_cast<const float4*>(sp + e);
+      s[e] = v.x; s[e + 1] = v.y; s[e + 2] = v.z; s[e + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) s[e] = (live && lane * EPL + e < D) ? sp[e] : 0.f;
+  }
+  const int half = rot / 2;
+  auto at = [](int i) { return i + PAD * (i / EPL); };      // where dimension i lies in a padded row
+  // A staging unit is a rotated pair (u, u + rot/2) for u < rot/2, or the single dimension
+  // rot + (u - rot/2) beyond; unit x of a chunk belongs to token x / DPAD.
+  const int units = half + (DPAD - rot);
+  // raw values wait in registers unconverted, so that nothing has to wait for them before its time
+  T rq0[RMAX], rq1[RMAX], rk0[RMAX], rk1[RMAX], rv[VMAX];
+  float pq0[RMAX], pq1[RMAX], pk0[RMAX], pk1[RMAX];         // the same from `prepared` (float32, final)
+  auto fetch = [&](int c0, int n) {
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) {
+      const int x = tid + r * kLaThreads, t = x / DPAD, u = x - t * DPAD;
+      if (prepared) { pq0[r] = pq1[r] = pk0[r] = pk1[r] = 0.f; }
+      else { rq0[r] = rq1[r] = rk0[r] = rk1[r] = from_float<T>(0.f); }
+      if (t < n && u < units) {
+        const int i0 = u < half ? u : rot + (u - half);
+        if (prepared) {
+          const float* row = prepared + (size_t)(row0 + c0 + t) * 2 * H * D + (size_t)head * D;
+          if (i0 < D) { pq0[r] = row[i0]; pk0[r] = row[H * D + i0]; }
+          if (u < half) { pq1[r] = row[u + half]; pk1[r] = row[H * D + u + half]; }
+        } else {
+          const T* row = src + (size_t)(row0 + c0 + t) * ld + (size_t)head * D;
+          if (i0 < D) { rq0[r] = row[q_col0 + i0]; rk0[r] = row[k_col0 + i0]; }
+          if (u < half) { rq1[r] = row[q_col0 + u + half]; rk1[r] = row[k_col0 + u + half]; }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < VMAX; ++r) {
+      const int x = tid + r * kLaThreads, t = x / COLS, j = x - t * COLS;
+      rv[r] = from_float<T>(0.f);
+      if (t < n && col0 + j < V) rv[r] = src[(size_t)(row0 + c0 + t) * ld + v_col0 + (size_t)head * V + col0 + j];
+    }
+  };
+  auto stage = [&](int c0, int n) {
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) {
+      const int x = tid + r * kLaThreads, t = x / DPAD, u = x - t * DPAD;
+      if (t < n && u < units) {
+        const int i0 = u < half ? u : rot + (u - half);     // (dimensions from D to DPAD hold zeros)
+        if (prepared) {
+          sq[t][at(i0)] = pq0[r];
+          sk[t][at(i0)] = pk0[r];
+          if (u < half) { sq[t][at(u + half)] = pq1[r]; sk[t][at(u + half)] = pk1[r]; }
+        } else if (u < half) {
+          float a, b, c, d;
+          la_turn(la_act(to_float(rq0[r]), use_silu), la_act(to_float(rq1[r]), use_silu), la_act(to_float(rk0[r]), use_silu),
+                  la_act(to_float(rk1[r]), use_silu), (float)(pos0 + c0 + t) * inv_freq[u], k_scale, a, b, c, d);
+          sq[t][at(u)] = a; sq[t][at(u + half)] = b;
+          sk[t][at(u)] = c; sk[t][at(u + half)] = d;
+        } else {
+          sq[t][at(i0)] = la_act(to_float(rq0[r]), use_silu);
+          sk[t][at(i0)] = __fmul_rn(la_act(to_float(rk0[r]), use_silu), k_scale);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < VMAX; ++r) {
+      const int x = tid + r * kLaThreads, t = x / COLS, j = x - t * COLS;
+      if (t < n) sv[t][j] = la_act(to_float(rv[r]), use_silu);
+    }
+  };
+  fetch(0, min(CH, rows));
+  for (int c0 = 0; c0 < rows; c0 += CH) {
+    const int n = min(CH, rows - c0);
+    __syncthreads();                                       // the previous chunk has been read
+    stage(c0, n);
+    __syncthreads();
+    if (c0 + CH < rows) fetch(c0 + CH, min(CH, rows - c0 - CH));      // in flight during the token loop
+    const float* kq0 = &sk[0][lane * (EPL + PAD)];
+    const float* qq0 = &sq[0][lane * (EPL + PAD)];
+#pragma unroll 2
+    for (int t = 0; t < n; ++t) {
+      const float v = sv[t][cidx];
+      const float* kr = kq0 + t * DP;
+      const float* qr = qq0 + t * DP;
+      float o = 0.f;
+      if (VEC) {
+#pragma unroll
+        for (int e = 0; e < EPL; e += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + e);
+          s[e] = fmaf(g, s[e], k4.x * v);         o = fmaf(s[e], q4.x, o);
+          s[e + 1] = fmaf(g, s[e + 1], k4.y * v); o = fmaf(s[e + 1], q4.y, o);
+          s[e + 2] = fmaf(g, s[e + 2], k4.z * v); o = fmaf(s[e + 2], q4.z, o);
+          s[e + 3] = fmaf(g, s[e + 3], k4.w * v); o = fmaf(s[e + 3], q4.w, o);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          s[e] = fmaf(g, s[e], kr[e] * v);
+          o = fmaf(s[e], qr[e], o);
+        }
+      }
+#pragma unroll
+      for (int w = LANES / 2; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (live && lane == 0) out[(size_t)(row0 + c0 + t) * H * V + (size_t)head * V + col] = o;
+    }
+  }
+  if (live) {
+    if (vec_state) {
+#pragma unroll
+      for (int e = 0; e < EPL; e += 4)
+        if (lane * EPL + e < D) *reinterpret_cast<float4*>(sp + e) = make_float4(s[e], s[e + 1], s[e + 2], s[e + 3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e)
+        if (lane * EPL + e < D) sp[e] = s[e];
+    }
+  }
+}
+
+template <typename T, int EPL, int LANES, int CH>
 static void launch_la(const void* src, int ld, int q0, int k0, int v0, const float* decay, const float* inv_freq,
                       int rot, float k_scale, int use_silu, float* state, long long slot_stride, const int* seg_row0,
                       const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D, int V,
-                      cudaStream_t stream) {
-  dim3 grid(S, H, (V + kLaCols - 1) / kLaCols);
-  launch_chained(decay_linear_attention_kernel<T, EPL>, grid, dim3(kLaLanes * kLaCols), 0, stream, (const T*)src, ld,
+                      const float* prepared, cudaStream_t stream) {
+  constexpr int COLS = kLaThreads / LANES;
+  dim3 grid(S, H, (V + COLS - 1) / COLS);
+  launch_chained(decay_linear_attention_kernel<T, EPL, LANES, CH>, grid, dim3(kLaThreads), 0, stream, (const T*)src, ld,
                  q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, (long)slot_stride, seg_row0, seg_slot,
-                 seg_pos0, out, H, D, V);
+                 seg_pos0, out, H, D, V, prepared);
 }
 
 template <typename T>
 static int dispatch_la(const void* src, int ld, int q0, int k0, int v0, const float* decay, const float* inv_freq,
                        int rot, float k_scale, int use_silu, float* state, long long slot_stride, const int* seg_row0,
                        const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D, int V,
-                       cudaStream_t stream) {
-#define NF_LA(E)                                                                                                   \
-  launch_la<T, E>(src, ld, q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, slot_stride, seg_row0,      \
-                  seg_slot, seg_pos0, out, S, H, D, V, stream)
-  if (D <= 8) NF_LA(1);
-  else if (D <= 16) NF_LA(2);
-  else if (D <= 32) NF_LA(4);
-  else if (D <= 64) NF_LA(8);
-  else if (D <= 128) NF_LA(16);
-  else NF_LA(32);
+                       const float* prepared, cudaStream_t stream) {
+#define NF_LA(E, L, C)                                                                                             \
+  launch_la<T, E, L, C>(src, ld, q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, slot_stride, seg_row0, \
+                        seg_slot, seg_pos0, out, S, H, D, V, prepared, stream)
+  if (D <= 8) NF_LA(1, 8, 16);
+  else if (D <= 16) NF_LA(2, 8, 16);
+  else if (D <= 32) NF_LA(4, 8, 16);
+  else if (D <= 64) NF_LA(8, 8, 16);
+  else if (D <= 128) NF_LA(8, 16, 16);
+  else NF_LA(16, 16, 8);
 #undef NF_LA
   return check_launch("decay_linear_attention");
 }
@@ -150,19 +262,36 @@ extern "C" int nf_decay_linear_attention_max_dim() { return 256; }
 
 // src [T, ld] holds q at q_col0 (H x D), k at k_col0 (H x D), v at v_col0 (H x V); decay float32 [H];
 // inv_freq float32 [rot / 2] (rot 0: nothing is turned); state float32, slot s at state + s * slot_stride,
-// [H][V][D]; out float32 [T, H * V].
+// [H][V][D]; out float32 [T, H * V].  prepared: null, or what nf_linear_attention_prepare made of the
+// same rows (q and k are then taken from there as they are).
 extern "C" int nf_decay_linear_attention(const void* src, int ld, int q_col0, int k_col0, int v_col0,
                                          const float* decay, const float* inv_freq, int rot, float k_scale,
                                          int use_silu, float* state, long long slot_stride, const int* seg_row0,
                                          const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D,
-                                         int V, int dtype, cudaStream_t stream) {
+                                         int V, int dtype, const float* prepared, cudaStream_t stream) {
   if (S == 0) return 0;
   NF_REQUIRE(S > 0 && H > 0 && D > 0 && V > 0 && D <= 256, "linear attention: bad sizes S=%d H=%d D=%d V=%d", S, H, D, V);
   NF_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "linear attention: rot=%d with D=%d", rot, D);
-  NF_REQUIRE(H <= 65535 && (V + kLaCols - 1) / kLaCols <= 65535, "linear attention: too many heads or columns");
+  NF_REQUIRE(H <= 65535 && (V + 7) / 8 <= 65535, "linear attention: too many heads or columns");
   if (dtype == kF32)
     return dispatch_la<float>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, use_silu, state,
-                              slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, stream);
+                              slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, stream);
   return dispatch_la<__nv_bfloat16>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, use_silu, state,
-                                    slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, stream);
+                                    slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, stream);
+}
+
+// out float32 [T, 2 H D]: q then k of every row, activated, turned by positions[t] and (k) scaled.
+extern "C" int nf_linear_attention_prepare(const void* src, int ld, int q_col0, int k_col0, const float* inv_freq, int rot,
+                                           float k_scale, int use_silu, const int* positions, float* out, int T, int H,
+                                           int D, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && H > 0 && D > 0 && rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq),
+             "linear attention prepare: bad sizes T=%d H=%d D=%d rot=%d", T, H, D, rot);
+  const int units = H * (rot / 2 + D - rot);
+  const dim3 grid(T, (units + 1023) / 1024 < 1 ? 1 : (units + 1023) / 1024);
+  if (dtype == kF32)
+    launch_chained(linear_attention_prepare_kernel<float>, grid, dim3(256), 0, stream, (const float*)src, ld, q_col0, k_col0, inv_freq, rot, k_scale, use_silu, positions, out, H, D);
+  else
+    launch_chained(linear_attention_prepare_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)src, ld, q_col0, k_col0, inv_freq, rot, k_scale, use_silu, positions, out, H, D);
+  return check_launch("linear_attention_prepare");
 }

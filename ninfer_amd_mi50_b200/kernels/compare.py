@@ -2,6 +2,7 @@
 every kernel of one step timed by name against its roofline.
 
     python bench.py --config vekasun
+    python bench.py --config difavik
 
 For each named size a Vekasun model (latent attention and state-space mixers alternating, routed
 experts scored by a sigmoid and weighted on their input) and a Qwen2-MoE model of the same width,
@@ -41,6 +42,26 @@ def vekasun_config(s: dict) -> dict:
     kinds = ["latent_attention", "mamba2", "mamba2", "latent_attention"]
     return {"architecture": "Vekasun", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "logit_scale": 1.0,
             "layers": [{"type": k, "mixer": att if k == "latent_attention" else ssm, "mlp": mlp} for k in kinds]}
+
+
+# the Difavik design at the same sizes: a window of 1,024 keys that keeps the first four, retention heads of
+# 64 x 128, lightning heads of 128 x 128
+WINDOW, KEEP_FIRST, RET_DIM = 1024, 4, 64
+
+
+def difavik_config(s: dict) -> dict:
+    H = s["heads"]
+    decay = [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H)]
+    left = {"heads": H, "kv_heads": H, "dim": HEAD_DIM, "vdim": HEAD_DIM, "scale": HEAD_DIM ** -0.5,
+            "mask": {"size": WINDOW, "keep_first": KEEP_FIRST}}
+    right = {"heads": H, "dim": RET_DIM, "vdim": HEAD_DIM, "decay": decay, "rot": {"base": 10000.0, "dims": RET_DIM}}
+    light = {"heads": H, "dim": HEAD_DIM, "vdim": HEAD_DIM, "decay": decay}
+    mlp = {"kind": "moe", "expert": {"ff": s["ff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]}}
+    kinds = ["lightning", "parallel", "parallel", "lightning"]
+    return {"architecture": "Difavik", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [{"type": k, "mixer": light if k == "lightning" else {"left": left, "right": right}, "mlp": mlp}
+                       for k in kinds]}
 
 
 def qwen2_moe_config(s: dict) -> dict:
@@ -91,9 +112,21 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
     state = s["ssm_heads"] * SSM_HEAD_DIM * N * 4
     D = HEAD_DIM
 
-    def phase(T, pairs, rows_ctx, nseg):
-        # pairs: sum over rows of the keys each sees; rows_ctx: cache tokens that must be read once
+    def phase(T, pairs, rows_ctx, nseg, pairs_w=0.0, rows_w=0):
+        # pairs: sum over rows of the keys each sees; rows_ctx: cache tokens that must be read once;
+        # pairs_w, rows_w: the same under the Difavik comparison's window
+        la = lambda Dk, Dv: (T * H * (2 * Dk + Dv) * 2 + T * H * Dv * 4 + 2 * nseg * H * Dk * Dv * 4, 4.0 * T * H * Dk * Dv)
+        windowed = (rows_w * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs_w)
         return {
+            "nf_prefill_attention_biased": windowed,
+            "nf_paged_attention_generic": windowed,
+            # two shapes share the kernel (lightning 128 x 128, retention 64 x 128): the mean of the two
+            "nf_decay_linear_attention": tuple((a + b) / 2 for a, b in zip(la(D, D), la(RET_DIM, D))),
+            "nf_scaled_norm_add": (T * W * (4 + 4 + 3 + 2), 0.0),
+            "nf_mean_of_rmsnorms": (T * W * (2 + 2 + 4), 0.0),
+            "nf_group_rmsnorm_gate": (T * H * D * (4 + 2 + 2), 0.0),
+            "nf_qk_whole_norm_append": (T * 2 * H * D * (4 + 2) + T * H * D * 2, 0.0),
+            "nf_pair_hash_embed": (T * W * (2 + 4 + 4), 0.0),
             "nf_latent_attention_generic": (rows_ctx * Wl * 2 + 2 * T * H * R * 2, 2.0 * H * (Wl + R) * pairs),
             "nf_latent_attention_mma": (rows_ctx * Wl * 2 + 2 * T * H * R * 2, 2.0 * H * (Wl + R) * pairs),
             "nf_prefill_attention_tc": (rows_ctx * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs),
@@ -115,8 +148,10 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
             "nf_gather_rows": (T * s["top"] * W * 4, 0.0),
         }
 
-    return {"prefill": phase(prompt, prompt * (prompt + 1) / 2, prompt, 1),
-            "decode": phase(batch, batch * (context + 1), batch * (context + 1), batch)}
+    seen = lambda p: min(p + 1, WINDOW) + max(0, min(KEEP_FIRST, p + 1 - WINDOW))       # keys position p sees
+    return {"prefill": phase(prompt, prompt * (prompt + 1) / 2, prompt, 1, float(sum(seen(p) for p in range(prompt))), prompt),
+            "decode": phase(batch, batch * (context + 1), batch * (context + 1), batch, float(batch * seen(context)),
+                            batch * seen(context))}
 
 
 def measure(config: dict, prompt: int, batch: int, context: int, steps: int, warmup: int) -> dict:
@@ -193,15 +228,18 @@ def measure(config: dict, prompt: int, batch: int, context: int, steps: int, war
     return out
 
 
+DESIGNS = {"vekasun": vekasun_config, "difavik": difavik_config}
+
+
 def run_comparison(sizes, peaks: dict, prompt: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32,
-                   warmup: int = 8) -> dict:
+                   warmup: int = 8, design: str = "vekasun") -> dict:
     klib.load()
     result = {}
     for name in sizes:
         s = SIZES[name]
         models = work_models(s, prompt, batch, context)
         entry = {}
-        for design, cfg in (("vekasun", vekasun_config(s)), ("qwen2_moe", qwen2_moe_config(s))):
+        for design, cfg in ((design, DESIGNS[design](s)), ("qwen2_moe", qwen2_moe_config(s))):
             t0 = time.time()
             m = measure(cfg, prompt, batch, context, steps, warmup)
             for ph in ("prefill", "decode"):
