@@ -72,7 +72,8 @@ __global__ void linear_attention_prepare_kernel(const T* __restrict__ src, int l
   }
 }
 
-template <typename T, int EPL, int LANES, int CH>    // D <= LANES * EPL; CH tokens staged at a time
+// PREP: q and k come from `prepared` (float32, final; D a multiple of 4), four dimensions a copy.
+template <typename T, int EPL, int LANES, int CH, bool PREP>    // D <= LANES * EPL; CH tokens staged at a time
 __global__ void __launch_bounds__(kLaThreads)
 decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0, int v_col0,
                               const float* __restrict__ decay, const float* __restrict__ inv_freq, int rot,
@@ -118,21 +119,29 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
   // rot + (u - rot/2) beyond; unit x of a chunk belongs to token x / DPAD.
   const int units = half + (DPAD - rot);
   // raw values wait in registers unconverted, so that nothing has to wait for them before its time
-  T rq0[RMAX], rq1[RMAX], rk0[RMAX], rk1[RMAX], rv[VMAX];
-  float pq0[RMAX], pq1[RMAX], pk0[RMAX], pk1[RMAX];         // the same from `prepared` (float32, final)
+  constexpr int RRAW = PREP ? 1 : RMAX;
+  constexpr int RP = PREP ? (CH * (DPAD / 4) + kLaThreads - 1) / kLaThreads : 1;
+  T rq0[RRAW], rq1[RRAW], rk0[RRAW], rk1[RRAW], rv[VMAX];
+  float4 fq[RP], fk[RP];
   auto fetch = [&](int c0, int n) {
+    if constexpr (PREP) {
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      const int x = tid + r * kLaThreads, t = x / DPAD, u = x - t * DPAD;
-      if (prepared) { pq0[r] = pq1[r] = pk0[r] = pk1[r] = 0.f; }
-      else { rq0[r] = rq1[r] = rk0[r] = rk1[r] = from_float<T>(0.f); }
-      if (t < n && u < units) {
-        const int i0 = u < half ? u : rot + (u - half);
-        if (prepared) {
-          const float* row = prepared + (size_t)(row0 + c0 + t) * 2 * H * D + (size_t)head * D;
-          if (i0 < D) { pq0[r] = row[i0]; pk0[r] = row[H * D + i0]; }
-          if (u < half) { pq1[r] = row[u + half]; pk1[r] = row[H * D + u + half]; }
-        } else {
+      for (int r = 0; r < RP; ++r) {
+        const int x = tid + r * kLaThreads, t = x / (DPAD / 4), i = 4 * (x - t * (DPAD / 4));
+        fq[r] = fk[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < n && i < D) {
+          const float* row = prepared + (size_t)(row0 + c0 + t) * 2 * H * D + (size_t)head * D + i;
+          fq[r] = *reinterpret_cast<const float4*>(row);
+          fk[r] = *reinterpret_cast<const float4*>(row + (size_t)H * D);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) {
+        const int x = tid + r * kLaThreads, t = x / DPAD, u = x - t * DPAD;
+        rq0[r] = rq1[r] = rk0[r] = rk1[r] = from_float<T>(0.f);
+        if (t < n && u < units) {
+          const int i0 = u < half ? u : rot + (u - half);
           const T* row = src + (size_t)(row0 + c0 + t) * ld + (size_t)head * D;
           if (i0 < D) { rq0[r] = row[q_col0 + i0]; rk0[r] = row[k_col0 + i0]; }
           if (u < half) { rq1[r] = row[q_col0 + u + half]; rk1[r] = row[k_col0 + u + half]; }
@@ -147,24 +156,31 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
     }
   };
   auto stage = [&](int c0, int n) {
+    if constexpr (PREP) {
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      const int x = tid + r * kLaThreads, t = x / DPAD, u = x - t * DPAD;
-      if (t < n && u < units) {
-        const int i0 = u < half ? u : rot + (u - half);     // (dimensions from D to DPAD hold zeros)
-        if (prepared) {
-          sq[t][at(i0)] = pq0[r];
-          sk[t][at(i0)] = pk0[r];
-          if (u < half) { sq[t][at(u + half)] = pq1[r]; sk[t][at(u + half)] = pk1[r]; }
-        } else if (u < half) {
-          float a, b, c, d;
-          la_turn(la_act(to_float(rq0[r]), use_silu), la_act(to_float(rq1[r]), use_silu), la_act(to_float(rk0[r]), use_silu),
-                  la_act(to_float(rk1[r]), use_silu), (float)(pos0 + c0 + t) * inv_freq[u], k_scale, a, b, c, d);
-          sq[t][at(u)] = a; sq[t][at(u + half)] = b;
-          sk[t][at(u)] = c; sk[t][at(u + half)] = d;
-        } else {
-          sq[t][at(i0)] = la_act(to_float(rq0[r]), use_silu);
-          sk[t][at(i0)] = __fmul_rn(la_act(to_float(rk0[r]), use_silu), k_scale);
+      for (int r = 0; r < RP; ++r) {
+        const int x = tid + r * kLaThreads, t = x / (DPAD / 4), i = 4 * (x - t * (DPAD / 4));
+        if (t < n) {                                       // (dimensions from D to DPAD get zeros)
+          *reinterpret_cast<float4*>(&sq[t][at(i)]) = fq[r];
+          *reinterpret_cast<float4*>(&sk[t][at(i)]) = fk[r];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) {
+        const int x = tid + r * kLaThreads, t = x / DPAD, u = x - t * DPAD;
+        if (t < n && u < units) {
+          const int i0 = u < half ? u : rot + (u - half);   // (dimensions from D to DPAD hold zeros)
+          if (u < half) {
+            float a, b, c, d;
+            la_turn(la_act(to_float(rq0[r]), use_silu), la_act(to_float(rq1[r]), use_silu), la_act(to_float(rk0[r]), use_silu),
+                    la_act(to_float(rk1[r]), use_silu), (float)(pos0 + c0 + t) * inv_freq[u], k_scale, a, b, c, d);
+            sq[t][at(u)] = a; sq[t][at(u + half)] = b;
+            sk[t][at(u)] = c; sk[t][at(u + half)] = d;
+          } else {
+            sq[t][at(i0)] = la_act(to_float(rq0[r]), use_silu);
+            sk[t][at(i0)] = __fmul_rn(la_act(to_float(rk0[r]), use_silu), k_scale);
+          }
         }
       }
     }
@@ -224,14 +240,14 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
   }
 }
 
-template <typename T, int EPL, int LANES, int CH>
+template <typename T, int EPL, int LANES, int CH, bool PREP>
 static void launch_la(const void* src, int ld, int q0, int k0, int v0, const float* decay, const float* inv_freq,
                       int rot, float k_scale, int use_silu, float* state, long long slot_stride, const int* seg_row0,
                       const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D, int V,
                       const float* prepared, cudaStream_t stream) {
   constexpr int COLS = kLaThreads / LANES;
   dim3 grid(S, H, (V + COLS - 1) / COLS);
-  launch_chained(decay_linear_attention_kernel<T, EPL, LANES, CH>, grid, dim3(kLaThreads), 0, stream, (const T*)src, ld,
+  launch_chained(decay_linear_attention_kernel<T, EPL, LANES, CH, PREP>, grid, dim3(kLaThreads), 0, stream, (const T*)src, ld,
                  q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, (long)slot_stride, seg_row0, seg_slot,
                  seg_pos0, out, H, D, V, prepared);
 }
@@ -240,16 +256,31 @@ template <typename T>
 static int dispatch_la(const void* src, int ld, int q0, int k0, int v0, const float* decay, const float* inv_freq,
                        int rot, float k_scale, int use_silu, float* state, long long slot_stride, const int* seg_row0,
                        const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D, int V,
-                       const float* prepared, cudaStream_t stream) {
-#define NF_LA(E, L, C)                                                                                             \
-  launch_la<T, E, L, C>(src, ld, q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, slot_stride, seg_row0, \
-                        seg_slot, seg_pos0, out, S, H, D, V, prepared, stream)
-  if (D <= 8) NF_LA(1, 8, 16);
-  else if (D <= 16) NF_LA(2, 8, 16);
-  else if (D <= 32) NF_LA(4, 8, 16);
-  else if (D <= 64) NF_LA(8, 8, 16);
-  else if (D <= 128) NF_LA(8, 16, 16);
-  else NF_LA(16, 16, 8);
+                       const float* prepared, int single, cudaStream_t stream) {
+#define NF_LA(E, L, C, P)                                                                                          \
+  launch_la<T, E, L, C, P>(src, ld, q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, slot_stride, seg_row0, \
+                           seg_slot, seg_pos0, out, S, H, D, V, prepared, stream)
+  // single: every segment brings one row (a decode step): one token staged at a time, few registers
+  if (prepared) {
+    if (D <= 32) NF_LA(4, 8, 16, true);
+    else if (D <= 64) NF_LA(8, 8, 16, true);
+    else if (D <= 128) NF_LA(8, 16, 16, true);
+    else NF_LA(16, 16, 8, true);
+  } else if (single) {
+    if (D <= 8) NF_LA(1, 8, 1, false);
+    else if (D <= 16) NF_LA(2, 8, 1, false);
+    else if (D <= 32) NF_LA(4, 8, 1, false);
+    else if (D <= 64) NF_LA(8, 8, 1, false);
+    else if (D <= 128) NF_LA(8, 16, 1, false);
+    else NF_LA(16, 16, 1, false);
+  } else {
+    if (D <= 8) NF_LA(1, 8, 16, false);
+    else if (D <= 16) NF_LA(2, 8, 16, false);
+    else if (D <= 32) NF_LA(4, 8, 16, false);
+    else if (D <= 64) NF_LA(8, 8, 16, false);
+    else if (D <= 128) NF_LA(8, 16, 16, false);
+    else NF_LA(16, 16, 8, false);
+  }
 #undef NF_LA
   return check_launch("decay_linear_attention");
 }
@@ -263,21 +294,23 @@ extern "C" int nf_decay_linear_attention_max_dim() { return 256; }
 // src [T, ld] holds q at q_col0 (H x D), k at k_col0 (H x D), v at v_col0 (H x V); decay float32 [H];
 // inv_freq float32 [rot / 2] (rot 0: nothing is turned); state float32, slot s at state + s * slot_stride,
 // [H][V][D]; out float32 [T, H * V].  prepared: null, or what nf_linear_attention_prepare made of the
-// same rows (q and k are then taken from there as they are).
+// same rows (q and k are then taken from there as they are; D a multiple of 4 above 16).  single != 0:
+// every segment brings one row.
 extern "C" int nf_decay_linear_attention(const void* src, int ld, int q_col0, int k_col0, int v_col0,
                                          const float* decay, const float* inv_freq, int rot, float k_scale,
                                          int use_silu, float* state, long long slot_stride, const int* seg_row0,
                                          const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D,
-                                         int V, int dtype, const float* prepared, cudaStream_t stream) {
+                                         int V, int dtype, const float* prepared, int single, cudaStream_t stream) {
   if (S == 0) return 0;
   NF_REQUIRE(S > 0 && H > 0 && D > 0 && V > 0 && D <= 256, "linear attention: bad sizes S=%d H=%d D=%d V=%d", S, H, D, V);
   NF_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "linear attention: rot=%d with D=%d", rot, D);
   NF_REQUIRE(H <= 65535 && (V + 7) / 8 <= 65535, "linear attention: too many heads or columns");
+  NF_REQUIRE(!prepared || (D % 4 == 0 && D > 16 && (uintptr_t)prepared % 16 == 0), "linear attention: prepared q and k need D a multiple of 4 above 16");
   if (dtype == kF32)
     return dispatch_la<float>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, use_silu, state,
-                              slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, stream);
+                              slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, single, stream);
   return dispatch_la<__nv_bfloat16>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, use_silu, state,
-                                    slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, stream);
+                                    slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, single, stream);
 }
 
 // out float32 [T, 2 H D]: q then k of every row, activated, turned by positions[t] and (k) scaled.

@@ -1227,7 +1227,8 @@ def decay_linear_attention(src: torch.Tensor, q_col0: int, k_col0: int, v_col0: 
     T = src.shape[0]
     out = torch.empty((T, heads * V), dtype=torch.float32, device=src.device)
     prepared = None
-    if not getattr(ctx, "all_single", False):
+    single = bool(getattr(ctx, "all_single", False))
+    if not single and D % 4 == 0 and D > 16:
         # a step with prompt portions: q and k are activated, turned and scaled once for all the CTAs of a head
         # (same arithmetic as inside the recurrence kernel, which does it itself for single rows)
         prepared = torch.empty((T, 2 * heads * D), dtype=torch.float32, device=src.device)
@@ -1237,7 +1238,7 @@ def decay_linear_attention(src: torch.Tensor, q_col0: int, k_col0: int, v_col0: 
     _lib.call("nf_decay_linear_attention", _p(src), c_int(src.shape[1]), c_int(q_col0), c_int(k_col0), c_int(v_col0),
               _p(decay), _p(inv_freq) if rot else None, c_int(rot), c_float(k_scale), c_int(1 if silu else 0),
               _p(state), c_longlong(state.stride(0)), _p(ctx.seg_row0), _p(ctx.seg_slot), _p(ctx.seg_pos0), _p(out),
-              c_int(ctx.S), c_int(heads), c_int(D), c_int(V), c_int(_dt(src)), _p(prepared), _stream())
+              c_int(ctx.S), c_int(heads), c_int(D), c_int(V), c_int(_dt(src)), _p(prepared), c_int(1 if single else 0), _stream())
     return out
 
 
