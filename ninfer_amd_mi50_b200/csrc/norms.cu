@@ -277,6 +277,40 @@ __global__ void scaled_norm_add_kernel(float* __restrict__ h, const TD* __restri
   }
 }
 
+// The same with the routed experts' pending sum as the sublayer's output:
+// d = sum_j wts[t, j] * y[inv[t * k + j]] (j ascending; wts null: unit weights), rounded to T as the separate
+// combine kernel rounds it, so both ways give the same bits.  The row is kept in shared memory.
+template <typename T, typename TO>
+__global__ void routed_scaled_norm_add_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ inv,
+                                              const float* __restrict__ wts, int k, const float* __restrict__ w,
+                                              const float* __restrict__ ls, float eps, TO* __restrict__ out, int hidden) {
+  extern __shared__ float row[];      // [hidden]
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  chain_release_if_small();
+  chain_wait(h, y, inv, wts);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int p = inv[r * k + j];
+      acc += (wts ? wts[r * k + j] : 1.f) * to_float(y[(size_t)p * hidden + i]);
+    }
+    const float d = to_float(from_float<T>(acc));
+    row[i] = d;
+    ss += d * d;
+  }
+  const float invr = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+  float* hr = h + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = row[i] * invr * w[i];
+    if (ls) v *= ls[i];
+    v += hr[i];
+    hr[i] = v;
+    if (out) out[(size_t)r * hidden + i] = from_float<TO>(v);
+  }
+}
+
 // out[t] = (1 / n) * sum_m (x_m[t] / rms(x_m[t])) * w_m: the mean of several mixers' outputs, each
 // first over its own root mean square and times its own weight.  out is float32.
 struct NormedInputs {
@@ -356,6 +390,29 @@ extern "C" int nf_scaled_norm_add(float* h, const void* delta, int delta_dtype, 
   else { if (out_dtype == kF32) NF_SNA(__nv_bfloat16, float); else NF_SNA(__nv_bfloat16, __nv_bfloat16); }
 #undef NF_SNA
   return check_launch("scaled_norm_add");
+}
+
+// y [pairs, hidden] of `dtype`, inv int32 [R * k], wts float32 [R, k] or null; out (may be null) has out_dtype.
+extern "C" int nf_routed_scaled_norm_add(float* h, const void* y, const int* inv, const float* wts, int k, int dtype,
+                                         const float* w, const float* ls, float eps, void* out, int out_dtype, int R,
+                                         int hidden, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && hidden > 0 && k > 0 && h && y && inv && w, "routed_scaled_norm_add: bad arguments");
+  const size_t smem = (size_t)hidden * sizeof(float);
+  NF_REQUIRE(smem <= 160 * 1024, "routed_scaled_norm_add: a row of %d does not fit shared memory", hidden);
+  const dim3 grid(R), block(norm_threads(hidden));
+#define NF_RSNA(T, TO)                                                                                              \
+  do {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(routed_scaled_norm_add_kernel<T, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_chained(routed_scaled_norm_add_kernel<T, TO>, grid, block, smem, stream, h, (const T*)y, inv, wts, k, w, ls, eps, \
+                   (TO*)out, hidden);                                                                               \
+  } while (0)
+  if (dtype == kF32) NF_RSNA(float, float);
+  else if (out_dtype == kF32) NF_RSNA(__nv_bfloat16, float);
+  else NF_RSNA(__nv_bfloat16, __nv_bfloat16);
+#undef NF_RSNA
+  return check_launch("routed_scaled_norm_add");
 }
 
 extern "C" int nf_mean_of_rmsnorms(const void* const* xs, const float* const* ws, int n, float eps, float* out, int R,

@@ -239,7 +239,7 @@ def run_comparison(sizes, peaks: dict, prompt: int = 2048, batch: int = 8, conte
         s = SIZES[name]
         models = work_models(s, prompt, batch, context)
         entry = {}
-        for design, cfg in ((design, DESIGNS[design](s)), ("qwen2_moe", qwen2_moe_config(s))):
+        for which, cfg in ((design, DESIGNS[design](s)), ("qwen2_moe", qwen2_moe_config(s))):
             t0 = time.time()
             m = measure(cfg, prompt, batch, context, steps, warmup)
             for ph in ("prefill", "decode"):
@@ -254,7 +254,7 @@ def run_comparison(sizes, peaks: dict, prompt: int = 2048, batch: int = 8, conte
                     table[k] = row
                 m["kernels"][ph] = table
             m["seconds"] = round(time.time() - t0)
-            entry[design] = m
+            entry[which] = m
         result[name] = entry
     return result
 

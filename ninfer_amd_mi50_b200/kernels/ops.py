@@ -1139,6 +1139,22 @@ def scaled_norm_add(h: torch.Tensor, delta: torch.Tensor, bias: Optional[torch.T
     return out
 
 
+def routed_scaled_norm_add(h: torch.Tensor, y: torch.Tensor, inv: torch.Tensor, wts: Optional[torch.Tensor], k: int,
+                           weight: torch.Tensor, scale: Optional[torch.Tensor], eps: float,
+                           out_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """`scaled_norm_add` whose delta is the routed experts' pending sum, sum_j wts[t, j] * y[inv[t * k + j]]
+    (rounded to y's type, as `moe_combine` rounds it), added up inside the kernel."""
+    _chk(h, "h", torch.float32); _chk(y, "y"); _chk(inv, "inv", torch.int32); _chk(weight, "weight", torch.float32)
+    for t, n in ((wts, "wts"), (scale, "scale")):
+        if t is not None:
+            _chk(t, n, torch.float32)
+    out = torch.empty(h.shape, dtype=out_dtype, device=h.device) if out_dtype is not None else None
+    _lib.call("nf_routed_scaled_norm_add", _p(h), _p(y), _p(inv), _p(wts), c_int(k), c_int(_dt(y)), _p(weight),
+              _p(scale), c_float(eps), _p(out), c_int(_dt(out) if out is not None else 0), c_int(h.shape[0]),
+              c_int(h.shape[1]), _stream())
+    return out
+
+
 def mean_of_rmsnorms(xs, ws, eps: float) -> torch.Tensor:
     """float32 [T, W]: the mean over m of (xs[m] / rms(xs[m])) * ws[m]; one to four inputs of equal shape."""
     n = len(xs)

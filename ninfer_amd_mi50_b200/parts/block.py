@@ -132,5 +132,5 @@ class SublayerNormScaledBlock(Block):
             bias = None
             if isinstance(f, BiasedOutput):          # the norm's kernel adds the bias in its own pass
                 f, bias = f.y, f.bias
-            x = self.norm2.add_scaled_norm(h, summed(f), self.scale2, copy_dtype, bias=bias)
+            x = self.norm2.add_scaled_norm(h, f, self.scale2, copy_dtype, bias=bias)
         return StreamCopy(x)

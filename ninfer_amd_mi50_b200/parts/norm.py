@@ -45,6 +45,12 @@ class RmsNorm(Norm):
     def add_scaled_norm(self, h, delta, scale, out_dtype, bias=None):
         """h += scale * norm(delta + bias) (in place, 32-bit): the norm sits on a sublayer's output,
         not on its input.  Returns the updated stream in `out_dtype` (None: nothing)."""
+        if isinstance(delta, RoutedSum):
+            if delta.shared is None and bias is None and delta.plan.top_k <= kernels.FUSED_COMBINE_MAX_K:
+                # the experts' weighted sum is added up inside the norm's kernel
+                return kernels.routed_scaled_norm_add(h, delta.y, delta.plan.inv, delta.wts, delta.plan.top_k,
+                                                      self.weight, scale, self.eps, out_dtype)
+            delta = summed(delta)
         return kernels.scaled_norm_add(h, delta, bias, self.weight, scale, self.eps, out_dtype)
 
     def weight_bytes(self) -> int:

@@ -416,3 +416,34 @@ def test_trace_replay_program_runs_the_design(folder, tmp_path):
             assert torch.equal(arr[at:at + n], got[e["id"]][rows[e["id"]]:rows[e["id"]] + n]), (i, e["id"])
             at += n
             rows[e["id"]] += n
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,hidden,k", [(5, 96, 2), (70, 100, 1), (33, 2048, 4)])
+def test_the_norm_that_adds_up_the_experts_rows_gives_the_separate_kernels_bits(dtype, rows, hidden, k):
+    from ninfer_amd_mi50_b200 import kernels
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(rows)
+    y = torch.randn((rows * k, hidden), generator=gen).to(dtype).to(dev)
+    wts = torch.rand((rows, k), generator=gen).to(dev)
+    idx = torch.stack([torch.randperm(7, generator=gen)[:k] for _ in range(rows)]).to(torch.int32).to(dev)
+    plan = kernels.moe_plan(idx, 7)
+    w = (1.0 + 0.1 * torch.randn(hidden, generator=gen)).to(dev)
+    ls = torch.randn(hidden, generator=gen).to(dev)
+    h0 = torch.randn((rows, hidden), generator=gen).to(dev)
+    out_dtype = None if dtype == torch.float32 else dtype
+    h1, h2 = h0.clone(), h0.clone()
+    x1 = kernels.scaled_norm_add(h1, kernels.moe_combine(y, plan, wts, None, None, dtype), None, w, ls, 1e-5, out_dtype)
+    x2 = kernels.routed_scaled_norm_add(h2, y, plan.inv, wts, k, w, ls, 1e-5, out_dtype)
+    assert torch.equal(h1, h2)
+    if out_dtype is not None:
+        assert torch.equal(x1, x2)
+    # and against plain arithmetic
+    d = torch.zeros((rows, hidden), dtype=torch.float64)
+    inv = plan.inv.cpu().long().reshape(rows, k)
+    for j in range(k):
+        d += wts.cpu().double()[:, j:j + 1] * y.cpu().double()[inv[:, j]]
+    d = d.to(dtype).double()
+    want = h0.cpu().double() + d / torch.sqrt((d * d).mean(dim=1, keepdim=True) + 1e-5) * w.cpu().double() * ls.cpu().double()
+    # (the sum is rounded to the experts' type before the norm: a bfloat16 step where the two sums straddle a rounding)
+    assert (h1.cpu().double() - want).abs().max() <= (2e-5 if dtype == torch.float32 else 1e-2) * want.abs().max()
