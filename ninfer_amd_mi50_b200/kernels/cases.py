@@ -187,7 +187,54 @@ def case_state_space(tokens: int, device, single: bool = False):
                                           (K - 1) * C, ctx, heads, P, N, G))]
 
 
+def case_linear_attention(tokens: int, device, single: bool = False, dim: int = 128, rotary: bool = False):
+    """The recurrence of a linear attention with a fixed decay per head (HQ heads of `dim` x 128): a prompt of
+    `tokens` rows, or `tokens` requests of one row.  `rotary`: q and k are turned and k scaled (retention);
+    otherwise q, k, v pass SiLU (lightning)."""
+    from . import decay_linear_attention, group_rmsnorm_gate, GATE_SIGMOID
+    V = 128
+    ctx = _one_request(tokens, device, single)
+    if not single:
+        ctx.seg_pos0 = torch.zeros(1, dtype=torch.int32, device=device)
+    else:
+        ctx.seg_pos0 = torch.full((tokens,), 2048, dtype=torch.int32, device=device)
+    proj = (torch.randn(tokens, 2 * HQ * dim + 2 * HQ * V, device=device) * 0.5).bfloat16()
+    state = torch.zeros(ctx.S + 1, HQ * V * dim, device=device)
+    decay = torch.full((HQ,), 0.97, device=device)
+    inv = torch.rand(dim // 2, device=device)
+    w = torch.ones(HQ * V, device=device)
+    run = lambda: decay_linear_attention(proj, 0, HQ * dim, 2 * HQ * dim, decay, inv if rotary else None,
+                                         dim if rotary else 0, dim ** -0.5 if rotary else 1.0, not rotary, state, ctx,
+                                         HQ, dim, V)
+    o = run()
+    return [("decay_linear_attention", run),
+            ("group_rmsnorm_gate", lambda: group_rmsnorm_gate(o, proj, 2 * HQ * dim + HQ * V, w, 1e-6, 1, GATE_SIGMOID,
+                                                              torch.bfloat16))]
+
+
+def case_window_attention(tokens: int, device, single: bool = False, context: int = 0, window: int = 1024, keep: int = 4):
+    """Softmax attention with a distance slope per head, a window that keeps the first `keep` keys and a head
+    gate (HQ query and key heads of 128): a prompt of `tokens` rows, or `tokens` decoded rows at `context`."""
+    from . import biased_window_attention
+    D = 128
+    ctx = _one_request(tokens, device, single, context)
+    held = (context + 1) if single else tokens
+    per = (held + PAGE - 1) // PAGE
+    pages = (torch.randn(ctx.S * per + 1, 2, HQ, PAGE, D, device=device) * 0.5).bfloat16()
+    bt = torch.arange(ctx.S * per, dtype=torch.int32, device=device).view(ctx.S, per)
+    q = (torch.randn(tokens, HQ * D, device=device) * 0.5).bfloat16()
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / HQ) for h in range(HQ)], device=device)
+    gate = torch.randn(tokens, HQ, device=device)
+    return [("biased_window_attention", lambda: biased_window_attention(q, HQ, HQ, D, pages, bt, PAGE, ctx, window, keep,
+                                                                        D ** -0.5, slopes, gate, 0))]
+
+
 CASES = {
+    "linear_attention_prefill": lambda dev: case_linear_attention(2048, dev),
+    "linear_attention_decode8": lambda dev: case_linear_attention(8, dev, True),
+    "retention_prefill": lambda dev: case_linear_attention(2048, dev, dim=64, rotary=True),
+    "window_attention_prefill": lambda dev: case_window_attention(2048, dev),
+    "window_attention_decode8": lambda dev: case_window_attention(8, dev, True, 2048),
     "latent_attention_prefill": lambda dev: case_latent_attention(2048, dev),
     "latent_attention_decode8": lambda dev: case_latent_attention(8, dev, True, 2048),
     "state_space_prefill": lambda dev: case_state_space(2048, dev),

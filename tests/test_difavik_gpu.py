@@ -197,7 +197,7 @@ def test_lightning_alone_whole_and_in_portions(tmp_path, dtype, heads, dim, vdim
 @pytest.mark.parametrize("left,right", [
     (DC.attention(4, 2, 16, 0.5, 7, 2), DC.retention(2, 16, 8, [0.9, 0.99], 100.0, 16)),
     (DC.attention(2, 2, 8, 0.9, 33, 0), DC.retention(3, 12, 20, [0.5, 0.75, 0.95], 10000.0, 4)),
-    (DC.attention(6, 1, 24, 0.3, 16, 16), DC.retention(1, 64, 64, [0.999], 1e6, 64)),
+    (DC.attention(6, 1, 24, 0.3, 16, 16), DC.retention(1, 64, 64, [0.9985], 5e5, 64)),
 ])
 def test_each_side_of_the_parallel_mixer_alone(tmp_path, dtype, side, left, right):
     """The other side's weight after its norm is zero, so the mean holds one side only."""
@@ -267,7 +267,7 @@ def plain_attention_rows(q, keys, vals, pos, scale, slopes, window, keep_first):
 
 @pytest.mark.parametrize("dtype,D,general", [(torch.float32, 16, True), (torch.bfloat16, 16, False), (torch.bfloat16, 64, False),
                                              (torch.bfloat16, 16, True), (torch.bfloat16, 24, True)])
-@pytest.mark.parametrize("window,keep_first", [(40, 6), (16, 16), (17, 0), (64, 1), (3, 70)])
+@pytest.mark.parametrize("window,keep_first", [(37, 5), (16, 16), (17, 0), (64, 1), (3, 70)])
 def test_one_loud_key_is_heard_just_inside_and_not_just_outside_every_edge(monkeypatch, dtype, D, general, window, keep_first):
     """The cache is filled by hand: every key is faint but one, whose score towers.  Placed just
     inside the window, on a page's border, among the kept first tokens or far back, it must take the
@@ -313,7 +313,7 @@ def test_one_loud_key_is_heard_just_inside_and_not_just_outside_every_edge(monke
                 assert (out[i] - want).abs().max() <= tol * max(1.0, want.abs().max()), (loud, p, window, keep_first)
             seen = (pos - loud < window) or loud < keep_first
             share = plain_attention_rows(q_all[pos].double(), keys, vals, pos, 0.7, slopes.double(), window, keep_first)
-            if seen and pos - loud < 40:
+            if seen and pos - loud < 37:
                 # the loud key takes (nearly) the whole output of the heads whose slope leaves it loud
                 assert (share[H - 1] - vals[loud, G - 1]).abs().max() < 1e-3
 
