@@ -447,3 +447,45 @@ def test_the_norm_that_adds_up_the_experts_rows_gives_the_separate_kernels_bits(
     want = h0.cpu().double() + d / torch.sqrt((d * d).mean(dim=1, keepdim=True) + 1e-5) * w.cpu().double() * ls.cpu().double()
     # (the sum is rounded to the experts' type before the norm: a bfloat16 step where the two sums straddle a rounding)
     assert (h1.cpu().double() - want).abs().max() <= (2e-5 if dtype == torch.float32 else 1e-2) * want.abs().max()
+
+
+@pytest.mark.parametrize("how", ["folder", "seed"])
+def test_the_command_line_generates_from_the_design(tmp_path, how):
+    """`bin/ninfer` on a Difavik folder, and on a folder with only config.json and a seed."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg0, seed = DC.CONFIGS["borrowing"]
+    d = str(tmp_path / "m")
+    DC.write_folder(cfg0, seed, d)
+    cfg, w = DC.read_folder(d)
+    if how == "seed":
+        os.remove(os.path.join(d, "model.safetensors"))
+    prompt = random_tokens(30, cfg["vocab"], 12)
+    cmd = [sys.executable, os.path.join(root, "bin", "ninfer"), d, "--prompt-ids", ",".join(map(str, prompt)),
+           "--temperature", "0", "--max-new", "6", "--dtype", "fp32", "--prefill-chunk", "16", "--repeat-penalty", "1"]
+    if how == "seed":
+        cmd += ["--random-weights", str(seed)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    got = [int(x) for x in p.stdout.split()]
+    assert len(got) == 6
+    seq = list(prompt)
+    for t in got:
+        lg = PD.forward(seq, w, cfg)[-1]
+        assert float(lg[t]) >= float(lg.max()) - 1e-4 * float(lg.abs().max())
+        seq.append(t)
+
+
+def test_sampled_generation_and_a_request_preempted_and_recomputed(folder):
+    """Sampling with a temperature through the scheduler, with a pool so small that a request is
+    preempted and recomputed: the pair table's previous token and the linear attentions' states
+    start again from nothing, and the tokens are those of a roomy pool."""
+    from ninfer_amd_mi50_b200.api import Ninfer
+    name, d, cfg, w, reqs = folder
+    prompts = [reqs["r0"][:50], reqs["r3"], reqs["r5"][:60]]
+    roomy = Ninfer(d, max_context=128, prefill_chunk=32, num_sequences=3, dtype="float32", page_size=16)
+    want = roomy.generate(prompts, max_new_tokens=24, temperature=0.8, top_k=20, seed=5)
+    tight = Ninfer(d, max_context=128, prefill_chunk=32, num_sequences=3, dtype="float32", page_size=16, cache_tokens=160)
+    got = tight.generate(prompts, max_new_tokens=24, temperature=0.8, top_k=20, seed=5)
+    assert got == want
