@@ -17,6 +17,11 @@
 // aligned blocks that hold them are walked first, then the window's); `slopes` takes
 // slope_h * (p - j) off head h's score of key j; `gate` multiplies head h's output by
 // sigmoid(gate[row, h]).
+// Steps of single rows (decode) may split a row's key blocks over several CTAs: the blocks of kept
+// first keys are one share, and every aligned group of a few window blocks (four: 256 keys, by
+// absolute position) another; each CTA leaves its unnormalised sum, maximum and denominator, and a
+// merge kernel adds the shares in ascending order.  Which blocks form a share depends on the row's
+// own position only, so the sums do not depend on what else the step holds.
 // Key blocks are aligned to multiples of 64 keys, so the order of a row's sums depends on
 // its own position only, not on how the prompt was cut.
 #include "common.cuh"
@@ -25,6 +30,7 @@ namespace nf {
 
 constexpr int kBQ = 64, kBKeys = 64;      // rows per tile (4 warps x 16), keys per block
 constexpr int kThreads = 128;
+int g_split_blocks = 4;                    // key blocks a share of a split row (aligned groups); nf_set_attention_split_blocks()
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ void pf_cp_async16(void* smem_dst, const void* gmem_src) {
@@ -61,7 +67,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
                          int page_size, int num_pages, int window, float scale,
                          const float* __restrict__ slopes, int keep_first, const float* __restrict__ gate,
-                         int gate_ld) {
+                         int gate_ld, int n_shares, float* __restrict__ part_o, float* __restrict__ part_ml,
+                         int kSplitBlocks) {
   constexpr int DS = D + 8;             // padded row stride in elements
   constexpr int LPR = D / 8;            // 16-byte pieces per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -88,6 +95,20 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   const int n_blocks = n_kept + (pos_last - kb_first) / kBKeys + 1;
   const float slope2 = slopes ? slopes[h] * kLog2e : 0.f;
   auto block_start = [&](int blk) { return blk < n_kept ? blk * kBKeys : kb_first + (blk - n_kept) * kBKeys; };
+  // this CTA's blocks: all of them, or (split rows) one share
+  int b0 = 0, b1 = n_blocks;
+  if (n_shares > 0) {
+    const int z = blockIdx.z;
+    if (z == 0) {
+      b1 = n_kept;
+    } else {
+      const int first_abs = kb_first / kBKeys;
+      const int grp = first_abs / kSplitBlocks + z - 1;                 // absolute group of window blocks
+      b0 = n_kept + max(0, grp * kSplitBlocks - first_abs);
+      b1 = min(n_blocks, n_kept + (grp + 1) * kSplitBlocks - first_abs);
+    }
+    if (b0 >= b1) break;                                                // an empty share writes nothing
+  }
 
   // ---- Q tile ------------------------------------------------------------------------------
   for (int c = threadIdx.x; c < kBQ * LPR; c += blockDim.x) {
@@ -133,14 +154,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   const int p_lo = pos_first + r_lo, p_hi = pos_first + r_hi;
   const int w_lo = window > 0 ? p_lo - window + 1 : 0, w_hi = window > 0 ? p_hi - window + 1 : 0;
 
-  load_block(0, 0);
+  load_block(b0, 0);
   pf_commit();
-  for (int blk = 0; blk < n_blocks; ++blk) {
-    if (blk + 1 < n_blocks) load_block(blk + 1, (blk + 1) & 1);
+  for (int blk = b0; blk < b1; ++blk) {
+    if (blk + 1 < b1) load_block(blk + 1, (blk + 1 - b0) & 1);
     pf_commit();
     pf_wait<1>();
     __syncthreads();
-    const __nv_bfloat16* Ks = KVs + (size_t)(blk & 1) * 2 * kBKeys * DS;
+    const __nv_bfloat16* Ks = KVs + (size_t)((blk - b0) & 1) * 2 * kBKeys * DS;
     const __nv_bfloat16* Vs = Ks + kBKeys * DS;
     const int kb = block_start(blk);
 
@@ -252,6 +273,17 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   for (int r = 0; r < 2; ++r) {
     const int row = r ? r_hi : r_lo;
     if (row >= n_rows) continue;
+    if (n_shares > 0) {
+      // a share of a split row: the unnormalised sum, the maximum (base-2 units) and the denominator
+      const size_t slot = ((size_t)(row0 + row) * Hq + h) * n_shares + blockIdx.z;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        part_o[slot * D + n * 8 + 2 * tq] = o[n][2 * r];
+        part_o[slot * D + n * 8 + 2 * tq + 1] = o[n][2 * r + 1];
+      }
+      if (tq == 0) { part_ml[slot * 2] = m_run[r]; part_ml[slot * 2 + 1] = l_run[r]; }
+      continue;
+    }
     float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
     if (gate) inv *= 1.f / (1.f + expf(-gate[(size_t)(row0 + row) * gate_ld + h]));
     __nv_bfloat16* dst = out + (size_t)(row0 + row) * Hq * D + (size_t)h * D;
@@ -265,24 +297,68 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   }  // which
 }
 
+// One CTA per (row, head) of a step of single rows: the row's shares in ascending order.
+__global__ void split_rows_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                        const int* __restrict__ positions, const int* __restrict__ tiles,
+                                        __nv_bfloat16* __restrict__ out, int Hq, int D,
+                                        int window, int keep_first, int n_shares, const float* __restrict__ gate,
+                                        int gate_ld, int kSplitBlocks) {
+  const int t = tiles[4 * blockIdx.x + 1], h = blockIdx.y;      // a tile is one row: its first row
+  chain_release_if_small();
+  const int pos = positions[t];
+  chain_wait(part_o, part_ml);
+  int lo = 0;
+  if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
+  const int kb_first = (lo / kBKeys) * kBKeys;
+  const int n_kept = (min(keep_first, kb_first) + kBKeys - 1) / kBKeys;
+  const int first_abs = kb_first / kBKeys, last_abs = pos / kBKeys;
+  const int z_last = min(n_shares - 1, last_abs / kSplitBlocks - first_abs / kSplitBlocks + 1);
+  const int z_first = n_kept > 0 ? 0 : 1;
+  const size_t base = ((size_t)t * Hq + h) * n_shares;
+  float m = -INFINITY;
+  for (int z = z_first; z <= z_last; ++z) m = fmaxf(m, part_ml[(base + z) * 2]);
+  float l = 0.f;
+  for (int z = z_first; z <= z_last; ++z) {
+    const float mz = part_ml[(base + z) * 2];
+    if (mz != -INFINITY) l += part_ml[(base + z) * 2 + 1] * exp2f(mz - m);
+  }
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (gate) inv *= 1.f / (1.f + expf(-gate[(size_t)t * gate_ld + h]));
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = z_first; z <= z_last; ++z) {
+      const float mz = part_ml[(base + z) * 2];
+      if (mz != -INFINITY) acc += part_o[(base + z) * D + d] * exp2f(mz - m);
+    }
+    out[((size_t)t * Hq + h) * D + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
 template <int D>
 static int launch_prefill(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                           int bt_width, const int* positions, const int* seg_row0, const int* tiles,
                           int n_tiles, void* out, int Hq, int Hkv, int page_size, int num_pages, int window,
                           float scale, const float* slopes, int keep_first, const float* gate, int gate_ld,
-                          cudaStream_t stream) {
+                          int n_shares, float* part_o, float* part_ml, cudaStream_t stream) {
   const size_t smem = (size_t)(kBQ + 4 * kBKeys) * (D + 8) * sizeof(__nv_bfloat16);
   static bool set = false;
   if (smem > 48 * 1024 && !set) {
     cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     set = true;
   }
-  dim3 grid(n_tiles, Hq);
+  dim3 grid(n_tiles, Hq, n_shares > 0 ? n_shares : 1);
   prefill_attention_kernel<D><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions,
       seg_row0, tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size, num_pages, window, scale, slopes, keep_first, gate,
-      gate_ld);
-  return check_launch("prefill_attention");
+      gate_ld, n_shares, part_o, part_ml, g_split_blocks);
+  if (int rc = check_launch("prefill_attention")) return rc;
+  if (n_shares > 0) {
+    launch_chained(split_rows_merge_kernel, dim3(n_tiles, Hq), dim3(D >= 64 ? 64 : 32), 0, stream, (const float*)part_o,
+                   (const float*)part_ml, positions, tiles, (__nv_bfloat16*)out, Hq, D, window, keep_first, n_shares, gate, gate_ld,
+                   g_split_blocks);
+    return check_launch("split_rows_merge");
+  }
+  return 0;
 }
 
 }  // namespace nf
@@ -291,22 +367,41 @@ using namespace nf;
 
 extern "C" int nf_prefill_attention_tile_rows() { return kBQ; }
 
+// Shares a split row can have: the kept keys' blocks, and the aligned groups of window blocks that the keys of a
+// row at a position below `max_context` can touch.
+extern "C" int nf_prefill_attention_shares(int window, int max_context) {
+  const int span = (window > 0 && window < max_context) ? window : max_context;      // keys a row sees at most
+  const int blocks = span / kBKeys + 2;                                             // (ragged at both ends)
+  return 1 + (blocks + g_split_blocks - 1) / g_split_blocks + 1;
+}
+
+// Key blocks (of 64 keys) a share of a split row holds; a power of two from 1 to 16.  For measurement: the
+// shares are aligned groups by absolute position, so a row's sums depend on this number and its position alone.
+extern "C" int nf_set_attention_split_blocks(int n) {
+  if (n == 1 || n == 2 || n == 4 || n == 8 || n == 16) g_split_blocks = n;
+  return g_split_blocks;
+}
+
 // bfloat16; head_dim a multiple of 16 up to 128.  `tiles` is int32 [n_ctas, 2, 2]: for every CTA two
 // tiles as (segment, first row), each at most 64 consecutive rows of one segment; the second may
 // be (-1, -1).  slopes float32 [Hq] or null; keep_first >= 0 (it counts only with a window); gate
-// float32 [T, gate_ld] (column h: head h's gate logit) or null.
+// float32 [T, gate_ld] (column h: head h's gate logit) or null.  n_shares > 0: every tile is one row, and a row's key blocks are split into shares (see the top of this file); n_shares must be at least
+// nf_prefill_attention_shares(window, longest context); part_o float32 [rows, Hq, n_shares, D], part_ml
+// [rows, Hq, n_shares, 2].
 extern "C" int nf_prefill_attention_biased(const void* qkv, int q_row_stride, const void* pages,
                                            const int* block_table, int bt_width, const int* positions,
                                            const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,
                                            int Hkv, int D, int page_size, int num_pages, int window, float scale,
                                            const float* slopes, int keep_first, const float* gate, int gate_ld,
-                                           cudaStream_t stream) {
+                                           int n_shares, float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  NF_REQUIRE(n_shares >= 0 && n_shares <= 65535 && (n_shares == 0 || (part_o && part_ml)),
+             "prefill attention: split rows need their workspace");
   NF_REQUIRE(n_tiles > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535, "prefill attention: bad sizes tiles=%d Hq=%d Hkv=%d", n_tiles, Hq, Hkv);
   NF_REQUIRE(q_row_stride % 8 == 0 && (uintptr_t)qkv % 16 == 0, "prefill attention: query rows must be 16-byte aligned");
   NF_REQUIRE(keep_first >= 0 && (!gate || gate_ld >= Hq), "prefill attention: bad options");
   if (window <= 0) keep_first = 0;
-#define NF_PF(DD) case DD: return launch_prefill<DD>(qkv, q_row_stride, pages, block_table, bt_width, positions, seg_row0, tiles, n_tiles, out, Hq, Hkv, page_size, num_pages, window, scale, slopes, keep_first, gate, gate_ld, stream);
+#define NF_PF(DD) case DD: return launch_prefill<DD>(qkv, q_row_stride, pages, block_table, bt_width, positions, seg_row0, tiles, n_tiles, out, Hq, Hkv, page_size, num_pages, window, scale, slopes, keep_first, gate, gate_ld, n_shares, part_o, part_ml, stream);
   switch (D) {
     NF_PF(16) NF_PF(32) NF_PF(48) NF_PF(64) NF_PF(80) NF_PF(96) NF_PF(112) NF_PF(128)
     default:
@@ -323,5 +418,5 @@ extern "C" int nf_prefill_attention(const void* qkv, int q_row_stride, const voi
                                     cudaStream_t stream) {
   return nf_prefill_attention_biased(qkv, q_row_stride, pages, block_table, bt_width, positions, seg_row0, tiles,
                                      n_tiles, out, Hq, Hkv, D, page_size, num_pages, window, scale, nullptr, 0, nullptr,
-                                     0, stream);
+                                     0, 0, nullptr, nullptr, stream);
 }

@@ -591,17 +591,26 @@ def biased_window_attention(q: torch.Tensor, Hq: int, Hkv: int, D: int, pages: t
     keep = keep_first if window > 0 else 0
     if (q.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic" and D in PREFILL_HEAD_DIMS
             and q.shape[1] % 8 == 0 and pages.is_contiguous()):
-        # the flash kernel on tensor cores: tiles of 64 rows of a segment, key blocks of 64
-        tiles = None
-        if getattr(ctx, "all_single", False) and getattr(ctx, "seg_len_host", None) is not None:
-            tiles, n_tiles = ctx.one_row_tiles()
-        elif getattr(ctx, "seg_len_host", None) is not None and getattr(ctx, "seg_pos0_host", None) is not None:
-            tiles, n_tiles = _tiles(ctx, PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK, True, 1)
-        if tiles is not None:
-            _lib.call("nf_prefill_attention_biased", _p(q), c_int(q.shape[1]), _p(pages), _p(block_table),
-                      c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles), c_int(n_tiles),
-                      _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size), c_int(pages.shape[0]), c_int(window),
-                      c_float(scale), _p(slopes), c_int(keep), gate_p, c_int(gate_ld), _stream())
+        # the flash kernel on tensor cores: tiles of 64 rows of a segment, key blocks of 64.  A segment of one row
+        # (a decoded token) has its key blocks split over several CTAs, whatever else the step holds.
+        if getattr(ctx, "seg_len_host", None) is not None and (ctx.all_single or getattr(ctx, "seg_pos0_host", None) is not None):
+            def flash(tiles, n_tiles, shares):
+                part_o = part_ml = None
+                if shares:
+                    part_o = torch.empty((T, Hq, shares, D), dtype=torch.float32, device=q.device)
+                    part_ml = torch.empty((T, Hq, shares, 2), dtype=torch.float32, device=q.device)
+                _lib.call("nf_prefill_attention_biased", _p(q), c_int(q.shape[1]), _p(pages), _p(block_table),
+                          c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles), c_int(n_tiles),
+                          _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size), c_int(pages.shape[0]), c_int(window),
+                          c_float(scale), _p(slopes), c_int(keep), gate_p, c_int(gate_ld), c_int(shares), _p(part_o),
+                          _p(part_ml), _stream())
+            singles, n_single = ctx.one_row_tiles()
+            if n_single:
+                flash(singles, n_single, int(_lib.load().nf_prefill_attention_shares(c_int(window), c_int(int(ctx.max_context)))))
+            if not ctx.all_single:
+                tiles, n_tiles = _tiles(ctx, PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK, True, 2 if n_single else 1)
+                if n_tiles:
+                    flash(tiles, n_tiles, 0)
             return out
     _lib.call("nf_paged_attention_generic", _p(q), c_int(q.shape[1]), _p(pages), _p(block_table),
               c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out), c_int(T), c_int(Hq),

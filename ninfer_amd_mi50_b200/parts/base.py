@@ -184,14 +184,23 @@ class StepContext:
         self._tiles[key] = (t, n_tiles)
         return t, n_tiles
 
-    def one_row_tiles(self) -> Tuple[torch.Tensor, int]:
-        """For a step whose every segment brings one row: a tile a segment, as the flash kernels take
-        them (int32 [S, 2, 2] of (segment, first row), the second entry (-1, -1)).  It depends on the
-        number of segments alone, so a step that is captured into a graph may use it: the tensor is
-        made on the first (uncaptured) run and kept."""
+    def one_row_tiles(self) -> Tuple[Optional[torch.Tensor], int]:
+        """A tile for every segment that brings exactly one row, as the flash kernels take them
+        (int32 [n, 2, 2] of (segment, first row), the second entry (-1, -1)); (None, 0) if there is
+        none.  When every segment brings one row it depends on the number of segments alone, so a
+        step that is captured into a graph may use it: the tensor is made on the first (uncaptured)
+        run and kept."""
         if "one_row" not in self._tiles:
-            flat = [v for s in range(self.S) for v in (s, s, -1, -1)]
-            self._tiles["one_row"] = (torch.tensor(flat, dtype=torch.int32).reshape(self.S, 2, 2).to(self.device), self.S)
+            if self.seg_len_host is None:
+                raise RuntimeError("one_row_tiles needs host segment lengths")
+            flat, row = [], 0
+            for s, n in enumerate(self.seg_len_host):
+                if n == 1:
+                    flat += [s, row, -1, -1]
+                row += n
+            n_tiles = len(flat) // 4
+            self._tiles["one_row"] = ((torch.tensor(flat, dtype=torch.int32).reshape(n_tiles, 2, 2).to(self.device), n_tiles)
+                                      if n_tiles else (None, 0))
         return self._tiles["one_row"]
 
     def single_rows(self) -> Tuple[Optional[torch.Tensor], int]:
